@@ -1,0 +1,489 @@
+"""`Buffer`: the DeepEP-style expert-parallel communication object.
+
+API parity (call shapes taken from the reference's call sites):
+  `Buffer(group, num_nvl_bytes, num_rdma_bytes)`, `.group/.num_nvl_bytes/.num_rdma_bytes`
+      `DeepEP_v1/deepep_v1_dispatch.py:35-56`
+  `Buffer.set_num_sms`, `Buffer.get_dispatch_config`, `Buffer.get_combine_config`
+      `DeepEP_v1/deepep_v1_dispatch.py:40-45,271`
+  `get_dispatch_layout`, `dispatch` (fresh and cached-handle), `combine`
+      `DeepEP_v1/deepep_v1_dispatch.py:199-230`, `DeepEP_v1/deepep_v1_combine.py:241-247`,
+      `DeepEP_Megatron/test_deepep_moe_dispatch_combine.py:107-132,158-165,200-206`
+
+How it works here (all data-path work is in the sm_100a kernels under csrc/ep):
+  1. `notify_send`  counts + stable positions of every item, count vectors stored to all peers.
+  2. `notify_wait`  bounded wait for the peers' counts, prefix sums -> exact destination rows;
+                    N_recv goes to pinned host memory (no device synchronise).
+  3. `dispatch_send` one pass over the local tokens: optional fp8 1x128 cast, 16-byte LSU
+                    stores straight into the final row of each destination's receive region.
+  4. bounded wait for the peers' done-flags; outputs are views (zero-copy) or clones.
+  Combine pushes rows back into per-item slots on the source and reduces them there.
+  Regions are double-buffered by epoch parity, flags are monotonically increasing epochs.
+
+Each op is split into phases (`_dispatch_p1/_p2/_p3`, `_combine_p1/_p2`) so that several
+virtual ranks living on ONE GPU (`LocalWorld`) can be driven phase by phase.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Tuple
+
+import torch
+
+from .. import _ext
+from ..utils.sizes import align_up
+from .config import Config, FIXED_BYTES, REGION_ALIGN
+from .events import EventHandle, EventOverlap
+from .symm import LocalWorld, ProcessWorld, SymmetricRegion
+
+STATUS_TEXT = {
+    0: "ok", 1: "timeout waiting for peers' token counts (notify)",
+    2: "timeout waiting for peers' dispatch-done flags", 3: "timeout waiting for peers' combine-done flags",
+    4: "timeout waiting for low-latency counts", 5: "timeout in barrier",
+    6: "receive region overflow (buffer too small for this routing)", 7: "expert index out of range",
+    8: "self-test wait timed out (expected)", 9: "timeout on an in-kernel mbarrier",
+    10: "combine slot overflow",
+}
+
+
+class EpTimeoutError(RuntimeError):
+    pass
+
+
+class EpStatusError(RuntimeError):
+    pass
+
+
+@dataclass
+class DispatchHandle:
+    """Everything combine / cached dispatch need. Opaque to callers."""
+    mode: int                      # 0 rank mode, 1 expert mode
+    T: int
+    H: int
+    K: int
+    E: int
+    n_recv: int
+    send_row: torch.Tensor         # [T,J] int32 row at the destination (-1 = not sent)
+    send_slot: torch.Tensor        # [T,J] int32 slot in my combine region (-1 = none)
+    meta: torch.Tensor             # int32 device metadata (counts, prefixes)
+    recv_meta: torch.Tensor        # [n_recv,2] int32 {slot at source, source rank}
+    topk_idx: Optional[torch.Tensor]
+    is_token_in_rank: Optional[torch.Tensor]
+    num_recv_tokens_per_expert_list: List[int] = field(default_factory=list)
+    fp8: bool = False
+    recv_prob: Optional[torch.Tensor] = None
+
+    @property
+    def n_recv_dev(self) -> torch.Tensor:
+        return self.meta[0:1]
+
+
+class _Carve:
+    """Byte offsets of every region for one (E, K, H, row bytes, combine row bytes) shape."""
+
+    def __init__(self, nbytes: int, R: int, E: int, K: int, H: int, row_bytes: int, comb_row_bytes: int):
+        C = _ext.load()
+        self.key = (E, K, H, row_bytes, comb_row_bytes)
+        self.flags = 0
+        off = align_up(C.NUM_CHANNELS * C.MAX_RANKS * 4, REGION_ALIGN)
+        csz = align_up(R * (R + E) * 4, REGION_ALIGN)
+        self.counts = (off, off + csz)
+        off += 2 * csz
+        self.ll_ctrl = off
+        if off > FIXED_BYTES // 2:
+            raise ValueError("too many experts/ranks for the fixed control area")
+        self.scale_cols = max(H // 128, 1)
+        sizes = dict(recv_x=row_bytes, recv_scales=self.scale_cols * 4, recv_topk_idx=K * 8,
+                     recv_topk_w=K * 4, recv_meta=8, recv_prob=4, comb_x=comb_row_bytes, comb_w=K * 4)
+        per_row = sum(sizes.values())
+        avail = nbytes - FIXED_BYTES - 2 * len(sizes) * REGION_ALIGN
+        self.cap = max(avail // (2 * per_row), 0)
+        self.slot_cap = self.cap
+        self.regions = []  # per parity: dict name -> offset
+        off = FIXED_BYTES
+        for _ in range(2):
+            d = {}
+            for name, sz in sizes.items():
+                d[name] = off
+                off = align_up(off + self.cap * sz, REGION_ALIGN)
+            self.regions.append(d)
+        assert off <= nbytes or self.cap == 0
+
+    def region_list(self, notify_parity: int, dispatch_parity: int, combine_parity: int):
+        d, c = self.regions[dispatch_parity], self.regions[combine_parity]
+        return [self.flags, self.counts[notify_parity], d["recv_x"], d["recv_scales"],
+                d["recv_topk_idx"], d["recv_topk_w"], d["recv_meta"], d["recv_prob"],
+                c["comb_x"], c["comb_w"]]
+
+
+_ELEM_DTYPE = {torch.bfloat16: "bfloat16", torch.float16: "float16", torch.float32: "float32"}
+
+
+class Buffer:
+    num_sms: int = 24
+
+    # ---- static configuration --------------------------------------------------------
+    @staticmethod
+    def set_num_sms(n: int) -> None:
+        if n <= 0:
+            raise ValueError("num_sms must be positive")
+        Buffer.num_sms = int(n)
+
+    @staticmethod
+    def get_dispatch_config(group_size: int, num_max_tokens_per_rank: int = 4096, num_topk: int = 8,
+                            num_experts: int = 256) -> Config:
+        return Config(Buffer.num_sms, num_max_tokens_per_rank, num_topk, num_experts)
+
+    @staticmethod
+    def get_combine_config(group_size: int, num_max_tokens_per_rank: int = 4096, num_topk: int = 8,
+                           num_experts: int = 256) -> Config:
+        return Config(Buffer.num_sms, num_max_tokens_per_rank, num_topk, num_experts)
+
+    # ---- construction ----------------------------------------------------------------
+    def __init__(self, group=None, num_nvl_bytes: int = 0, num_rdma_bytes: int = 0,
+                 low_latency_mode: bool = False, num_qps_per_rank: int = 1, *,
+                 world=None, timeout_s: float = 20.0, blocks_per_sm: int = 2):
+        self.C = _ext.load()
+        self.world = world if world is not None else ProcessWorld(group)
+        self.group = group
+        self.rank, self.group_size = self.world.rank, self.world.size
+        if self.group_size > self.C.MAX_RANKS:
+            raise ValueError(f"group size {self.group_size} exceeds {self.C.MAX_RANKS}")
+        self.num_nvl_bytes = int(num_nvl_bytes)
+        self.num_rdma_bytes = int(num_rdma_bytes)   # accepted, unused inside one NVLink domain
+        self.low_latency_mode = low_latency_mode
+        self.device = self.world.device
+        self.timeout_s = float(timeout_s)
+        self.blocks_per_sm = blocks_per_sm
+        if self.num_nvl_bytes < FIXED_BYTES * 2:
+            raise ValueError("num_nvl_bytes too small; use Config.get_nvl_buffer_size_hint")
+        self.region = SymmetricRegion(self.world, self.num_nvl_bytes)
+        with torch.cuda.device(self.device):
+            self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+            self.counters = torch.zeros(8, dtype=torch.int32, device=self.device)
+            self.comm_stream = (torch.cuda.current_stream() if self.world.local
+                                else torch.cuda.Stream(device=self.device))
+        self.host_word = self.C.host_mapped_alloc(4 * 4096)
+        self._epoch = dict(notify=0, dispatch=0, combine=0, barrier=0, ll_dispatch=0, ll_combine=0)
+        self._carve: Optional[_Carve] = None
+        self._ll = None
+        self.world.host_barrier()
+
+    def destroy(self):
+        if getattr(self, "region", None) is not None:
+            torch.cuda.synchronize(self.device)
+            self.world.host_barrier()
+            self.region.close()
+            self.region = None
+            self.C.host_mapped_free(self.host_word)
+            self.host_word = 0
+
+    # ---- helpers ---------------------------------------------------------------------
+    @property
+    def peers(self) -> List[int]:
+        return list(self.region.peer_ptrs)
+
+    @property
+    def status_ptr(self) -> int:
+        return self.status.data_ptr()
+
+    def _timeout_ns(self) -> int:
+        return int(self.timeout_s * 1e9)
+
+    def _blocks(self) -> int:
+        return max(1, Buffer.num_sms * self.blocks_per_sm)
+
+    def check_status(self) -> None:
+        """Synchronising read of the device status word; raises on any recorded fault."""
+        code = int(self.status[0].item())
+        if code != 0:
+            self.status.zero_()
+            cls = EpTimeoutError if code in (1, 2, 3, 4, 5, 8, 9) else EpStatusError
+            raise cls(f"b200ep status {code}: {STATUS_TEXT.get(code, 'unknown')}")
+
+    def _get_carve(self, E: int, K: int, H: int, row_bytes: int, comb_row_bytes: int) -> _Carve:
+        key = (E, K, H, row_bytes, comb_row_bytes)
+        if self._carve is None or self._carve.key != key:
+            if self._carve is not None:
+                self.barrier()           # region reuse with another shape: drain every rank first
+            self._carve = _Carve(self.num_nvl_bytes, self.group_size, E, K, H, row_bytes, comb_row_bytes)
+        return self._carve
+
+    def _geom(self, *, E, K, T, mode, H, cap, slot_cap, epoch) -> List[int]:
+        R = self.group_size
+        J, B = (R, R) if mode == 0 else (K, E)
+        return [self.rank, R, E, E // R, K, T, mode, J, B, H, cap, slot_cap, epoch, self._timeout_ns()]
+
+    def _enter(self, previous_event, allocate_on_comm_stream, async_finish):
+        if allocate_on_comm_stream and not async_finish:
+            raise ValueError("allocate_on_comm_stream=True requires async_finish=True")
+        compute = torch.cuda.current_stream(self.device)
+        if self.comm_stream != compute:
+            if previous_event is not None and getattr(previous_event, "event", None) is not None:
+                ev = previous_event.event.event
+                if ev is not None:
+                    self.comm_stream.wait_event(ev)
+            else:
+                self.comm_stream.wait_stream(compute)
+        return compute
+
+    def _exit(self, compute, async_finish, tensors) -> Optional[EventOverlap]:
+        if self.comm_stream == compute:
+            return EventOverlap(EventHandle(compute)) if async_finish else None
+        for t in tensors:
+            if isinstance(t, torch.Tensor) and t.is_cuda:
+                t.record_stream(compute)
+        if async_finish:
+            return EventOverlap(EventHandle(self.comm_stream), tuple(tensors))
+        compute.wait_stream(self.comm_stream)
+        return None
+
+    def barrier(self) -> None:
+        """Device-side barrier over the group on the communication stream."""
+        self._epoch["barrier"] += 1
+        with torch.cuda.stream(self.comm_stream):
+            self.C.barrier(self.peers, 0, self.rank, self.group_size, self._epoch["barrier"],
+                           self._timeout_ns(), self.status_ptr, not self.world.local)
+
+    def probe_timeout(self, timeout_s: float = 0.2) -> int:
+        """Wait on a flag that nothing sets, with a short limit; returns the status code that the
+        kernel recorded (8) and clears it. Shows that a lost peer ends in an error, not a hang."""
+        with torch.cuda.stream(self.comm_stream):
+            self.C.wait_flags(self.region.local_ptr, 0, self.C.NUM_CHANNELS - 1, 1, 1 << 30,
+                              int(timeout_s * 1e9), self.status_ptr, 8)
+        code = int(self.status[0].item())
+        self.status.zero_()
+        return code
+
+    # ---- layout ----------------------------------------------------------------------
+    def get_dispatch_layout(self, topk_idx: torch.Tensor, num_experts: int,
+                            previous_event=None, async_finish: bool = False,
+                            allocate_on_comm_stream: bool = False):
+        """-> (num_tokens_per_rank[R] i32, None, num_tokens_per_expert[E] i32,
+               is_token_in_rank[T,R] bool, event)"""
+        R = self.group_size
+        if num_experts % R:
+            raise ValueError("num_experts must be divisible by the group size")
+        if topk_idx.dtype != torch.int64:
+            topk_idx = topk_idx.to(torch.int64)
+        topk_idx = topk_idx.contiguous()
+        compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
+        with torch.cuda.stream(self.comm_stream):
+            T = topk_idx.shape[0]
+            per_rank = torch.empty(R, dtype=torch.int32, device=self.device)
+            per_expert = torch.empty(num_experts, dtype=torch.int32, device=self.device)
+            in_rank = torch.empty((T, R), dtype=torch.bool, device=self.device)
+            self.C.layout(topk_idx, num_experts, R, per_rank, per_expert, in_rank, self.status_ptr)
+        ev = self._exit(compute, async_finish, (per_rank, per_expert, in_rank, topk_idx))
+        return per_rank, None, per_expert, in_rank, ev
+
+    # ---- dispatch --------------------------------------------------------------------
+    def _dispatch_p1(self, x, handle, is_token_in_rank, num_tokens_per_expert, topk_idx,
+                     topk_weights, use_fp8, group_by_expert, num_experts):
+        R = self.group_size
+        if isinstance(x, tuple):
+            raise NotImplementedError(
+                "pre-quantised (fp8, scales) input is not supported: pass bf16 and use_fp8=True, "
+                "the cast is fused into the dispatch kernel")
+        if x.dim() != 2 or not x.is_contiguous():
+            raise ValueError("x must be a contiguous [num_tokens, hidden] tensor")
+        if x.dtype not in _ELEM_DTYPE:
+            raise ValueError(f"unsupported dtype {x.dtype}")
+        T, H = x.shape
+        st = dict(x=x, T=T, H=H, fp8=bool(use_fp8), cached=handle is not None)
+        if handle is not None:
+            if handle.T != T or handle.H != H:
+                raise ValueError("cached handle does not match x")
+            st.update(mode=handle.mode, K=handle.K, E=handle.E, handle=handle,
+                      topk_idx=handle.topk_idx, topk_weights=None)
+        else:
+            mode = 1 if group_by_expert else 0
+            if topk_idx is not None:
+                topk_idx = topk_idx.to(torch.int64).contiguous()
+            if topk_weights is not None:
+                topk_weights = topk_weights.to(torch.float32).contiguous()
+            if mode == 0 and is_token_in_rank is None:
+                raise ValueError("rank-mode dispatch needs is_token_in_rank (get_dispatch_layout)")
+            if mode == 1 and topk_idx is None:
+                raise ValueError("expert-grouped dispatch needs topk_idx")
+            if num_tokens_per_expert is not None:
+                E = int(num_tokens_per_expert.numel())
+            elif num_experts:
+                E = int(num_experts)
+            else:
+                raise ValueError("num_tokens_per_expert (or num_experts) is required")
+            K = int(topk_idx.shape[1]) if topk_idx is not None else 1
+            st.update(mode=mode, K=K, E=E, topk_idx=topk_idx, topk_weights=topk_weights,
+                      is_token_in_rank=is_token_in_rank, num_tokens_per_expert=num_tokens_per_expert)
+        mode, K, E = st["mode"], st["K"], st["E"]
+        if E % R:
+            raise ValueError("num_experts must be divisible by the group size")
+        row_bytes_out = H if st["fp8"] else H * x.element_size()
+        elem = 2 if st["fp8"] else x.element_size()
+        carve = self._get_carve(E, K, H, H * elem, H * elem)
+        st["carve"] = carve
+        if carve.cap <= 0:
+            raise ValueError("num_nvl_bytes too small for this hidden size")
+        J, B = (R, R) if mode == 0 else (K, E)
+        st.update(J=J, B=B, row_bytes_out=row_bytes_out)
+        if st["cached"]:
+            st["meta"] = handle.meta
+            st["send_row"], st["send_slot"] = handle.send_row, handle.send_slot
+            return st
+        self._epoch["notify"] += 1
+        st["epoch_n"] = self._epoch["notify"]
+        dev = self.device
+        C_chunks = max((T + self.C.CHUNK_TOKENS - 1) // self.C.CHUNK_TOKENS, 1)
+        st["item_rank"] = torch.empty((max(T, 1), J), dtype=torch.int32, device=dev)
+        st["chunk_hist"] = torch.empty((C_chunks, B), dtype=torch.int32, device=dev)
+        El = E // R
+        st["meta"] = torch.zeros(2 + El + (El + 1) + (R + 1) + 2 * B, dtype=torch.int32, device=dev)
+        st["send_row"] = torch.empty((max(T, 1), J), dtype=torch.int32, device=dev)
+        st["send_slot"] = torch.empty((max(T, 1), J), dtype=torch.int32, device=dev)
+        regions = carve.region_list(st["epoch_n"] & 1, 0, 0)
+        geom = self._geom(E=E, K=K, T=T, mode=mode, H=H, cap=carve.cap, slot_cap=carve.slot_cap,
+                          epoch=st["epoch_n"])
+        per_expert = st.get("num_tokens_per_expert")
+        if per_expert is not None and per_expert.dtype != torch.int32:
+            per_expert = per_expert.to(torch.int32)
+        self.C.notify_send(geom, regions, self.peers,
+                           st.get("is_token_in_rank") if mode == 0 else None,
+                           st["topk_idx"] if mode == 1 else None,
+                           per_expert if mode == 0 else None,
+                           st["item_rank"], st["chunk_hist"], self.counters[0:1], self.status_ptr)
+        return st
+
+    def _dispatch_p2(self, st):
+        carve = st["carve"]
+        self._epoch["dispatch"] += 1
+        st["epoch_d"] = self._epoch["dispatch"]
+        pn = (st.get("epoch_n", 0)) & 1
+        regions = carve.region_list(pn, st["epoch_d"] & 1, 0)
+        st["regions"] = regions
+        geom = self._geom(E=st["E"], K=st["K"], T=st["T"], mode=st["mode"], H=st["H"], cap=carve.cap,
+                          slot_cap=carve.slot_cap, epoch=st.get("epoch_n", 0))
+        if not st["cached"]:
+            self.C.notify_wait(geom, regions, self.region.local_ptr, st["meta"], self.host_word,
+                               self.status_ptr)
+        geom[12] = st["epoch_d"]
+        self.C.dispatch_send(geom, regions, self.peers, st["meta"], st["x"], st["fp8"], st["cached"],
+                             st["topk_idx"], st.get("topk_weights"), st.get("item_rank"),
+                             st.get("chunk_hist"), st["send_row"], st["send_slot"],
+                             self.counters[1:2], self.status_ptr, self._blocks())
+
+    def _dispatch_p3(self, st, zero_copy: bool):
+        R, E, K, H = self.group_size, st["E"], st["K"], st["H"]
+        El = E // R
+        carve = st["carve"]
+        if st["cached"]:
+            h = st["handle"]
+            n_recv, per_expert_list = h.n_recv, h.num_recv_tokens_per_expert_list
+        else:
+            if not self.C.host_wait_ge(self.host_word, 0, st["epoch_n"], self.timeout_s + 5.0):
+                raise EpTimeoutError("host timed out waiting for the receive count")
+            n_recv = self.C.host_read_i32(self.host_word, 1)
+            if n_recv < 0:
+                self.status.zero_()
+                raise EpTimeoutError("b200ep status 1: " + STATUS_TEXT[1])
+            if n_recv > carve.cap:
+                raise EpStatusError(f"receive region overflow: {n_recv} rows > capacity {carve.cap}")
+            per_expert_list = [self.C.host_read_i32(self.host_word, 2 + i) for i in range(El)]
+        self.C.wait_flags(self.region.local_ptr, 0, 1, R, st["epoch_d"], self._timeout_ns(),
+                          self.status_ptr, 2)
+        reg = dict(zip(("flags", "counts", "recv_x", "recv_scales", "recv_topk_idx", "recv_topk_w",
+                        "recv_meta", "recv_prob", "comb_x", "comb_w"), st["regions"]))
+        keep = (lambda t: t) if zero_copy else (lambda t: t.clone())
+        if st["fp8"]:
+            rx = self.region.view(reg["recv_x"], (n_recv, H), "float8_e4m3fn")
+            rs = self.region.view(reg["recv_scales"], (n_recv, H // 128), "float32")
+            recv_x = (keep(rx), keep(rs))
+        else:
+            recv_x = keep(self.region.view(reg["recv_x"], (n_recv, H), _ELEM_DTYPE[st["x"].dtype]))
+        if st["cached"]:
+            return recv_x, None, None, per_expert_list, st["handle"]
+        recv_topk_idx = recv_topk_w = recv_prob = None
+        if st["mode"] == 0 and st["topk_idx"] is not None:
+            recv_topk_idx = self.region.view(reg["recv_topk_idx"], (n_recv, K), "int64").clone()
+            recv_topk_w = self.region.view(reg["recv_topk_w"], (n_recv, K), "float32").clone()
+        if st["mode"] == 1:
+            recv_prob = self.region.view(reg["recv_prob"], (n_recv,), "float32").clone()
+        recv_meta = self.region.view(reg["recv_meta"], (n_recv, 2), "int32").clone()
+        handle = DispatchHandle(st["mode"], st["T"], H, K, E, n_recv, st["send_row"], st["send_slot"],
+                                st["meta"], recv_meta, st["topk_idx"], st.get("is_token_in_rank"),
+                                per_expert_list, st["fp8"], recv_prob)
+        return recv_x, recv_topk_idx, recv_topk_w, per_expert_list, handle
+
+    def dispatch(self, x, handle: Optional[DispatchHandle] = None, num_tokens_per_rank=None,
+                 num_tokens_per_rdma_rank=None, is_token_in_rank=None, num_tokens_per_expert=None,
+                 topk_idx=None, topk_weights=None, expert_alignment: int = 1, num_worst_tokens: int = 0,
+                 config: Optional[Config] = None, previous_event=None, async_finish: bool = False,
+                 allocate_on_comm_stream: bool = False, *, use_fp8: bool = False,
+                 group_by_expert: bool = False, zero_copy: bool = False, num_experts: int = 0):
+        """-> (recv_x | (recv_x_fp8, scales), recv_topk_idx, recv_topk_weights,
+               num_recv_tokens_per_expert_list, handle, event)
+
+        Rank mode (default): one row per (token, destination rank), rows ordered by source rank
+        then token; `recv_topk_idx` holds LOCAL expert ids, -1 where the expert lives elsewhere.
+        `group_by_expert=True`: one row per (token, expert), rows grouped by local expert;
+        the per-row router probability is in `handle.recv_prob`.
+        `zero_copy=True` returns views into the symmetric region that stay valid until the second
+        next dispatch on this buffer."""
+        compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
+        with torch.cuda.stream(self.comm_stream):
+            st = self._dispatch_p1(x, handle, is_token_in_rank, num_tokens_per_expert, topk_idx,
+                                   topk_weights, use_fp8, group_by_expert, num_experts)
+            self._dispatch_p2(st)
+            out = self._dispatch_p3(st, zero_copy)
+        flat = []
+        for o in out[:3]:
+            flat.extend(o if isinstance(o, tuple) else (o,))
+        ev = self._exit(compute, async_finish, [t for t in flat if t is not None] + [x])
+        return (*out, ev)
+
+    # ---- combine ---------------------------------------------------------------------
+    def _combine_p1(self, x, handle: DispatchHandle, topk_weights):
+        if x.dim() != 2 or not x.is_contiguous() or x.shape[1] != handle.H:
+            raise ValueError("x must be a contiguous [num_recv_tokens, hidden] tensor")
+        if x.shape[0] < handle.n_recv:
+            raise ValueError("x has fewer rows than the handle's receive count")
+        if x.dtype not in _ELEM_DTYPE:
+            raise ValueError(f"unsupported dtype {x.dtype}")
+        carve = self._carve
+        if carve is None or carve.key[:3] != (handle.E, handle.K, handle.H):
+            raise ValueError("combine must follow a dispatch of the same shape on this buffer")
+        if handle.H * x.element_size() > carve.key[4]:
+            raise ValueError("combine dtype is wider than the region reserved at dispatch")
+        self._epoch["combine"] += 1
+        ep = self._epoch["combine"]
+        regions = carve.region_list(0, 0, ep & 1)
+        geom = self._geom(E=handle.E, K=handle.K, T=handle.T, mode=handle.mode, H=handle.H,
+                          cap=handle.n_recv, slot_cap=carve.slot_cap, epoch=ep)
+        if topk_weights is not None:
+            topk_weights = topk_weights.to(torch.float32).contiguous()
+        self.C.combine_send(geom, regions, self.peers, handle.n_recv_dev, handle.recv_meta, x,
+                            topk_weights, self.counters[2:3], self.status_ptr, self._blocks())
+        return dict(ep=ep, regions=regions, geom=geom, dtype=x.dtype, with_w=topk_weights is not None)
+
+    def _combine_p2(self, st, handle: DispatchHandle, weights=None):
+        out = torch.empty((handle.T, handle.H), dtype=st["dtype"], device=self.device)
+        out_w = (torch.empty((handle.T, handle.K), dtype=torch.float32, device=self.device)
+                 if st["with_w"] else None)
+        self.C.combine_reduce(st["geom"], st["regions"], self.region.local_ptr, handle.send_slot,
+                              weights, out, out_w, st["ep"], self.status_ptr, self._blocks() * 2)
+        return out, out_w
+
+    def combine(self, x, handle: DispatchHandle, topk_weights=None, bias=None,
+                config: Optional[Config] = None, previous_event=None, async_finish: bool = False,
+                allocate_on_comm_stream: bool = False, *, item_weights=None):
+        """-> (combined_x[T,H], combined_topk_weights | None, event).
+        Unweighted sum over the rows that each token was sent to (an identity expert returns
+        x times the number of destinations, `DeepEP_v1/deepep_v1_combine.py:335-342`);
+        `item_weights[T,J]` (J = ranks in rank mode, top-k in expert mode) turns it into a
+        weighted reduction applied on arrival."""
+        compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
+        with torch.cuda.stream(self.comm_stream):
+            st = self._combine_p1(x, handle, topk_weights)
+            out, out_w = self._combine_p2(st, handle, item_weights)
+            if bias is not None:
+                out = out + (bias[0] if isinstance(bias, (tuple, list)) else bias)
+        ev = self._exit(compute, async_finish, [out, x] + ([out_w] if out_w is not None else []))
+        return out, out_w, ev

@@ -1,0 +1,55 @@
+"""Lock-step driver for several virtual ranks on ONE GPU (`LocalWorld`).
+
+A kernel that waits for a peer must not run concurrently with, or before, the kernel it waits
+for when both share a GPU. The driver therefore runs phase k of every virtual rank before
+phase k+1 of any rank, on one stream, so every wait finds its flag already set.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from .buffer import Buffer
+from .symm import LocalWorld
+
+
+class LocalGroup:
+    def __init__(self, size: int, num_nvl_bytes: int, device: Optional[torch.device] = None,
+                 timeout_s: float = 2.0):
+        self.size = size
+        worlds = LocalWorld.make(size, device)
+        self.buffers: List[Buffer] = [Buffer(None, num_nvl_bytes, world=w, timeout_s=timeout_s)
+                                      for w in worlds]
+
+    def get_dispatch_layout(self, topk_idx: Sequence[torch.Tensor], num_experts: int):
+        return [b.get_dispatch_layout(t, num_experts) for b, t in zip(self.buffers, topk_idx)]
+
+    def dispatch(self, xs, *, handles=None, layouts=None, topk_idx=None, topk_weights=None,
+                 use_fp8=False, group_by_expert=False, zero_copy=False, num_experts=0):
+        n = self.size
+        sts = []
+        for r, b in enumerate(self.buffers):
+            lay = layouts[r] if layouts is not None else (None, None, None, None, None)
+            sts.append(b._dispatch_p1(
+                xs[r], handles[r] if handles is not None else None, lay[3], lay[2],
+                topk_idx[r] if topk_idx is not None else None,
+                topk_weights[r] if topk_weights is not None else None,
+                use_fp8, group_by_expert, num_experts))
+        for r, b in enumerate(self.buffers):
+            b._dispatch_p2(sts[r])
+        return [b._dispatch_p3(sts[r], zero_copy) for r, b in enumerate(self.buffers)]
+
+    def combine(self, ys, handles, topk_weights=None, item_weights=None):
+        sts = [b._combine_p1(ys[r], handles[r], topk_weights[r] if topk_weights is not None else None)
+               for r, b in enumerate(self.buffers)]
+        return [b._combine_p2(sts[r], handles[r], item_weights[r] if item_weights is not None else None)
+                for r, b in enumerate(self.buffers)]
+
+    def check_status(self):
+        for b in self.buffers:
+            b.check_status()
+
+    def destroy(self):
+        for b in self.buffers:
+            b.destroy()

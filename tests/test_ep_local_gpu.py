@@ -1,0 +1,147 @@
+"""Single-GPU checks of the EP data path with several virtual ranks (one kernel set per rank,
+phases run in lock step). Every kernel result is compared with the fp32 PyTorch oracle."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from gpu_data_transfer_profile_b200.ref import cpu_oracle as O
+
+
+def _mk(R, T, H, E, K, dtype=torch.bfloat16, seed=0, zipf=0.0, uneven=False):
+    xs, idxs, ws = [], [], []
+    for r in range(R):
+        t = T + (7 * r if uneven else 0)
+        g = torch.Generator().manual_seed(seed * 100 + r)
+        xs.append(torch.randn(t, H, generator=g).to(dtype))
+        i, w = O.make_routing(t, E, K, seed * 100 + r, zipf)
+        idxs.append(i)
+        ws.append(w)
+    return xs, idxs, ws
+
+
+def _group(R, nbytes=256 << 20):
+    from gpu_data_transfer_profile_b200.parallel.local import LocalGroup
+    return LocalGroup(R, nbytes, timeout_s=2.0)
+
+
+@pytest.mark.parametrize("R,T,H,E,K", [(1, 64, 256, 8, 2), (2, 128, 256, 8, 2), (4, 200, 512, 32, 4),
+                                       (8, 96, 1024, 64, 8)])
+def test_layout_matches_oracle(R, T, H, E, K):
+    xs, idxs, ws = _mk(R, T, H, E, K)
+    g = _group(R, 64 << 20)
+    try:
+        lays = g.get_dispatch_layout([i.cuda() for i in idxs], E)
+        for r in range(R):
+            pr, pe, inr = O.layout_ref(idxs[r], E, R)
+            assert torch.equal(lays[r][0].cpu(), pr)
+            assert lays[r][1] is None
+            assert torch.equal(lays[r][2].cpu(), pe)
+            assert torch.equal(lays[r][3].cpu(), inr)
+        g.check_status()
+    finally:
+        g.destroy()
+
+
+@pytest.mark.parametrize("R,T,H,E,K,dtype", [
+    (1, 64, 256, 8, 2, torch.bfloat16), (2, 128, 256, 8, 2, torch.bfloat16),
+    (4, 200, 512, 32, 4, torch.bfloat16), (8, 96, 1024, 64, 8, torch.bfloat16),
+    (2, 128, 256, 8, 2, torch.float32), (4, 33, 384, 16, 3, torch.float16)])
+def test_dispatch_combine_rank_mode(R, T, H, E, K, dtype):
+    xs, idxs, ws = _mk(R, T, H, E, K, dtype, uneven=True)
+    g = _group(R)
+    try:
+        cx = [x.cuda() for x in xs]
+        ci = [i.cuda() for i in idxs]
+        cw = [w.cuda() for w in ws]
+        lays = g.get_dispatch_layout(ci, E)
+        outs = g.dispatch(cx, layouts=lays, topk_idx=ci, topk_weights=cw)
+        ref = O.dispatch_rank_mode_ref(xs, idxs, ws, E)
+        for d in range(R):
+            rx, ri, rw, cnt, h = outs[d]
+            ex, ei, ew, sr, stok, ecnt = ref[d]
+            assert rx.shape == ex.shape
+            assert torch.equal(rx.cpu(), ex)
+            assert torch.equal(ri.cpu(), ei)
+            assert torch.equal(rw.cpu(), ew)
+            assert cnt == ecnt
+            assert h.n_recv == ex.shape[0]
+        # combine with an "expert" that scales by (1 + rank): checks routing of every row
+        ys = [(outs[d][0].float() * (1 + d)).to(dtype) for d in range(R)]
+        comb = g.combine(ys, [o[4] for o in outs], topk_weights=[o[2] for o in outs])
+        cref = O.combine_ref([y.cpu() for y in ys], [r[3] for r in ref], [r[4] for r in ref],
+                             [x.shape[0] for x in xs])
+        wref = O.combine_ref([r[2] for r in ref], [r[3] for r in ref], [r[4] for r in ref],
+                             [x.shape[0] for x in xs])
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        for s in range(R):
+            got, got_w = comb[s]
+            torch.testing.assert_close(got.cpu().float(), cref[s], atol=tol * 8, rtol=tol)
+            torch.testing.assert_close(got_w.cpu(), wref[s], atol=1e-6, rtol=1e-6)
+        g.check_status()
+    finally:
+        g.destroy()
+
+
+@pytest.mark.parametrize("R,T,H,E,K", [(1, 64, 256, 8, 2), (2, 128, 256, 8, 2), (4, 100, 512, 32, 4),
+                                       (8, 64, 1024, 8, 2)])
+def test_dispatch_combine_expert_mode(R, T, H, E, K):
+    xs, idxs, ws = _mk(R, T, H, E, K, zipf=1.2)
+    g = _group(R)
+    try:
+        cx = [x.cuda() for x in xs]
+        ci = [i.cuda() for i in idxs]
+        cw = [w.cuda() for w in ws]
+        outs = g.dispatch(cx, topk_idx=ci, topk_weights=cw, group_by_expert=True, num_experts=E)
+        ref = O.dispatch_expert_mode_ref(xs, idxs, ws, E)
+        for d in range(R):
+            rx, _, _, cnt, h = outs[d]
+            ex, ep, sr, stok, sk, ecnt = ref[d]
+            assert cnt == ecnt
+            assert torch.equal(rx.cpu(), ex)
+            assert torch.equal(h.recv_prob.cpu(), ep)
+        # weighted combine: out[t] = sum_k w[t,k] * x[t]  == x[t] (weights sum to 1)
+        comb = g.combine([o[0] for o in outs], [o[4] for o in outs], item_weights=cw)
+        for s in range(R):
+            torch.testing.assert_close(comb[s][0].cpu().float(), xs[s].float(), atol=3e-2, rtol=2e-2)
+        g.check_status()
+    finally:
+        g.destroy()
+
+
+def test_dispatch_fp8_and_cached():
+    R, T, H, E, K = 4, 96, 1024, 32, 4
+    xs, idxs, ws = _mk(R, T, H, E, K)
+    g = _group(R)
+    try:
+        cx = [x.cuda() for x in xs]
+        ci = [i.cuda() for i in idxs]
+        cw = [w.cuda() for w in ws]
+        lays = g.get_dispatch_layout(ci, E)
+        outs = g.dispatch(cx, layouts=lays, topk_idx=ci, topk_weights=cw, use_fp8=True)
+        ref = O.dispatch_rank_mode_ref(xs, idxs, ws, E)
+        for d in range(R):
+            (q, s), _, _, _, h = outs[d]
+            eq, es = O.fp8_block_quant_ref(ref[d][0])
+            torch.testing.assert_close(s.cpu(), es, rtol=1e-6, atol=0)
+            deq = O.fp8_block_dequant_ref(q.cpu(), s.cpu())
+            torch.testing.assert_close(deq, ref[d][0].float(), atol=0.3, rtol=0.07)
+            assert (q.cpu().view(torch.uint8) != eq.view(torch.uint8)).float().mean() < 0.01
+        # cached-handle dispatch of new data reuses the layout
+        x2 = [torch.randn_like(x) for x in cx]
+        outs2 = g.dispatch(x2, handles=[o[4] for o in outs])
+        ref2 = O.dispatch_rank_mode_ref([x.cpu() for x in x2], idxs, ws, E)
+        for d in range(R):
+            assert torch.equal(outs2[d][0].cpu(), ref2[d][0])
+        g.check_status()
+    finally:
+        g.destroy()
+
+
+def test_lost_peer_is_an_error_not_a_hang():
+    g = _group(1, 8 << 20)
+    try:
+        assert g.buffers[0].probe_timeout(0.05) == 8
+        g.check_status()
+    finally:
+        g.destroy()

@@ -1,0 +1,106 @@
+"""CPU tests of size parsing and traffic-pattern arithmetic."""
+import argparse
+
+import pytest
+
+from gpu_data_transfer_profile_b200.utils import patterns as P
+from gpu_data_transfer_profile_b200.utils import sizes as S
+
+
+def test_parse_nbytes_units():
+    assert S.parse_nbytes("64K") == 65536
+    assert S.parse_nbytes("1M") == 1 << 20
+    assert S.parse_nbytes("1G") == 1 << 30
+    assert S.parse_nbytes("1.5MiB") == 1572864
+    assert S.parse_nbytes("2MB") == 2_000_000
+    assert S.parse_nbytes("8kib") == 8192
+    assert S.parse_nbytes("4096") == 4096
+    assert S.parse_nbytes(123) == 123
+    with pytest.raises(ValueError):
+        S.parse_nbytes("12Q")
+    with pytest.raises(ValueError):
+        S.parse_nbytes("abc")
+
+
+def test_fmt_bytes():
+    assert S.fmt_bytes(1024) == "1.00 KiB"
+    assert S.fmt_bytes(1536 * 1024) == "1.50 MiB"
+    assert S.fmt_bytes(10) == "10.00 B"
+
+
+def test_size_list_and_offsets():
+    assert S.parse_size_list("64K,128K,1M") == (65536, 131072, 1 << 20)
+    with pytest.raises(argparse.ArgumentTypeError):
+        S.parse_size_list("64K,,1M")
+    assert S.contiguous_offsets((10, 20, 30)) == (0, 10, 30)
+    sz = S.default_nonuniform_sizes(1 << 20, 4)
+    assert len(sz) == 4 and sum(sz) == 1 << 20 and len(set(sz)) == 4
+    assert all(s % 16 == 0 for s in sz)
+    assert S.pow2_sweep(4096, 65536) == (4096, 8192, 16384, 32768, 65536)
+    assert S.parse_gpu_ids("0,2,2,5", 8) == (0, 2, 5)
+    with pytest.raises(ValueError):
+        S.parse_gpu_ids("9", 8)
+
+
+def test_choose_pair():
+    assert P.choose_pair(3, 8, "ring") == (3, 4)
+    assert P.choose_pair(7, 8, "ring") == (7, 0)
+    assert P.choose_pair(0, 8, "reverse-ring") == (0, 7)
+    assert P.choose_pair(2, 8, "pair") == (2, 3)
+    assert P.choose_pair(3, 8, "pair") == (3, 2)
+    with pytest.raises(ValueError):
+        P.choose_pair(0, 3, "pair")
+    with pytest.raises(ValueError):
+        P.choose_pair(0, 4, "star")
+
+
+def test_destination_orders():
+    assert P.destination_order(2, 4, rotate=True) == (3, 0, 1)
+    assert P.destination_order(2, 4, rotate=False) == (0, 1, 3)
+    assert P.rr_destinations(1, 4, "ring") == (2, 3, 0)
+    assert P.rr_destinations(1, 4, "reverse-ring") == (0, 3, 2)
+    with pytest.raises(ValueError):
+        P.rr_destinations(0, 4, "pair")
+
+
+def test_round_robin_chunks_cover_range_once():
+    chunks = P.rr_chunks(100_000, 8192, 7)
+    assert sum(c[2] for c in chunks) == 100_000
+    assert [c[0] for c in chunks[:9]] == [0, 1, 2, 3, 4, 5, 6, 0, 1]
+    assert chunks[-1][1] + chunks[-1][2] == 100_000
+    assert P.rr_owner(8192 * 7 + 5, 8192, 7) == 0
+
+
+@pytest.mark.parametrize("layout", P.LAYOUTS)
+def test_gap_layout(layout):
+    lay = P.build_layout(layout, (100, 200, 300), gap=64)
+    sg = "src" in layout or "both" in layout
+    dg = "dst" in layout or "both" in layout
+    assert lay.src_offsets == ((0, 164, 428) if sg else (0, 100, 300))
+    assert lay.dst_offsets == ((0, 164, 428) if dg else (0, 100, 300))
+    assert lay.src_bytes == (728 if sg else 600)
+    assert lay.dst_gaps() == ([(100, 64), (364, 64)] if dg else [])
+
+
+def test_multi_source_plan():
+    sizes = P.msrc_sizes(4, 2, 1000)
+    plan = P.build_multi_source_plan(1, 4, sizes, source_gap=64)
+    assert plan.src_bytes == 2 * 3000 + 64
+    assert plan.dst_bytes == (2000, 2000, 2000)
+    assert [plan.peer(k) for k in range(3)] == [2, 3, 0]
+    b = list(plan.batches())
+    assert b[0][2] == [(0, 0, 1000), (3064, 1000, 1000)]
+    sizes = P.msrc_sizes(4, 2, 0, destination_sizes=(16, 32, 48))
+    assert sizes == ((16, 32, 48), (16, 32, 48))
+    sizes = P.msrc_sizes(4, 2, 0, source_sizes=(16, 32))
+    assert sizes == ((16, 16, 16), (32, 32, 32))
+    with pytest.raises(ValueError):
+        P.msrc_sizes(4, 2, 0, source_sizes=(1,))
+
+
+def test_fill_values_stay_below_sentinels():
+    for r in range(16):
+        for c in range(40):
+            assert P.layout_chunk_value(r, c) < P.SRC_GAP_SENTINEL
+            assert P.msrc_chunk_value(r, c, c % 7) < P.SRC_GAP_SENTINEL
+    assert P.pair_fill_value(3) != P.pair_prefill_value(3)
