@@ -1,0 +1,109 @@
+"""Rank runtime shared by every CLI: bootstrap, EP sub-groups, scalar reductions, ordered print.
+
+Parity: `get_rank_info/barrier/all_reduce_*` (`Copy_Engine/nvlink_copy_engine_test.py:384-410`),
+`init_distributed/create_ep_group/ordered_print/all_ranks_boolean`
+(`DeepEP_v1/deepep_v1_dispatch.py:124-154,251-262`). NCCL (or gloo on CPU) carries control
+traffic only; payload moves through this library's own kernels.
+"""
+from __future__ import annotations
+
+import os
+import sys
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def env_rank_info() -> Tuple[int, int, int]:
+    """(rank, world_size, local_rank) from the torchrun environment; (0, 1, LOCAL_RANK|0) without it."""
+    if "RANK" not in os.environ:
+        return 0, 1, int(os.environ.get("LOCAL_RANK", "0"))
+    return int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def init_distributed(backend: Optional[str] = None) -> Tuple[int, int, int]:
+    """Initialise torch.distributed when launched by torchrun; single process otherwise."""
+    rank, world, local = env_rank_info()
+    use_cuda = torch.cuda.is_available()
+    if use_cuda:
+        torch.cuda.set_device(local % max(torch.cuda.device_count(), 1))
+    if "RANK" in os.environ and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        kw = {}
+        if use_cuda:
+            kw["device_id"] = torch.device("cuda", torch.cuda.current_device())
+        dist.init_process_group(backend or ("nccl" if use_cuda else "gloo"), **kw)
+    return rank, world, local
+
+
+def is_dist() -> bool:
+    return dist.is_available() and dist.is_initialized()
+
+
+def barrier(group=None) -> None:
+    if is_dist():
+        dist.barrier(group=group)
+
+
+def _dev():
+    return torch.device("cuda", torch.cuda.current_device()) if (
+        torch.cuda.is_available() and is_dist() and dist.get_backend() == "nccl") else torch.device("cpu")
+
+
+def all_reduce_scalar(x: float, op: str = "max", group=None) -> float:
+    if not is_dist():
+        return float(x)
+    t = torch.tensor([x], dtype=torch.float64, device=_dev())
+    dist.all_reduce(t, op={"max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN,
+                           "sum": dist.ReduceOp.SUM}[op], group=group)
+    return float(t.item())
+
+
+def all_reduce_max_float(x: float, group=None) -> float:
+    return all_reduce_scalar(x, "max", group)
+
+
+def all_reduce_sum_float(x: float, group=None) -> float:
+    return all_reduce_scalar(x, "sum", group)
+
+
+def all_ranks_boolean(ok: bool, group=None) -> bool:
+    """True only if every rank passed (MIN-reduce of an int flag)."""
+    return all_reduce_scalar(1.0 if ok else 0.0, "min", group) > 0.5
+
+
+def create_ep_group(ep: int):
+    """Contiguous EP groups of `ep` ranks; returns (group or None, ep_rank, group_index).
+    Every rank must call this (new_group is collective for all groups)."""
+    if not is_dist():
+        if ep != 1:
+            raise ValueError("--ep > 1 needs a torchrun launch")
+        return None, 0, 0
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if ep <= 0 or world % ep:
+        raise ValueError(f"--ep {ep} must divide WORLD_SIZE {world}")
+    mine = None
+    for g in range(world // ep):
+        ranks = list(range(g * ep, (g + 1) * ep))
+        grp = dist.new_group(ranks)
+        if rank in ranks:
+            mine = grp
+    return mine, rank % ep, rank // ep
+
+
+def ordered_print(msg: str, group=None, file=sys.stdout) -> None:
+    """Print one message per rank in rank order."""
+    if not is_dist():
+        print(msg, file=file, flush=True)
+        return
+    for r in range(dist.get_world_size()):
+        if dist.get_rank() == r:
+            print(msg, file=file, flush=True)
+        dist.barrier()
+
+
+def shutdown() -> None:
+    if is_dist():
+        dist.destroy_process_group()
