@@ -166,4 +166,5 @@ def main() -> int:
 
 
 if __name__ == "__main__":
-    sys.exit(main())
+    from gpu_data_transfer_profile_b200.utils.dist import run_main
+    run_main(main)

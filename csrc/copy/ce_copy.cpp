@@ -42,15 +42,21 @@ CeEngine::CeEngine(std::vector<CeCopy> copies, int mode, int stream_device, bool
   cudaSetDevice(device_);
   cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking);
   if (mode_ == kGraph && !copies_.empty()) {
-    // Capture the N peer copies once; every iteration is then a single graph launch.
-    if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
-      for (const auto& c : copies_)
-        cudaMemcpyPeerAsync(reinterpret_cast<void*>(c.dst), c.dst_dev,
-                            reinterpret_cast<const void*>(c.src), c.src_dev, c.nbytes, stream_);
-      if (cudaStreamEndCapture(stream_, &graph_) == cudaSuccess && graph_ != nullptr)
-        cudaGraphInstantiate(&graph_exec_, graph_, 0);
+    // Build the graph explicitly: N independent 1-D memcpy nodes (no edges, so the copy
+    // engines may run them concurrently); every iteration is then a single graph launch.
+    cudaError_t e = cudaGraphCreate(&graph_, 0);
+    for (size_t i = 0; e == cudaSuccess && i < copies_.size(); ++i) {
+      const auto& c = copies_[i];
+      cudaGraphNode_t node;
+      e = cudaGraphAddMemcpyNode1D(&node, graph_, nullptr, 0, reinterpret_cast<void*>(c.dst),
+                                   reinterpret_cast<const void*>(c.src), c.nbytes, cudaMemcpyDefault);
     }
-    if (graph_exec_ == nullptr) { cudaGetLastError(); last_where_ = "graph capture/instantiate"; }
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&graph_exec_, graph_, 0);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      graph_exec_ = nullptr;
+      last_where_ = std::string("graph build: ") + cudaGetErrorString(e);
+    }
   }
   if (mode_ == kKernel && !copies_.empty()) {
     std::vector<CopyDesc> h(copies_.size());
@@ -89,7 +95,7 @@ int CeEngine::enqueue_once() {
     return 0;
   }
   if (mode_ == kGraph) {
-    if (graph_exec_ == nullptr) { last_where_ = "graph not instantiated"; return (int)cudaErrorInvalidValue; }
+    if (graph_exec_ == nullptr) { if (last_where_.empty()) last_where_ = "graph not instantiated"; return (int)cudaErrorInvalidValue; }
     cudaError_t e = cudaGraphLaunch(graph_exec_, stream_);
     if (e != cudaSuccess) last_where_ = "cudaGraphLaunch";
     return (int)e;

@@ -47,8 +47,10 @@ combine_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, const int* __restric
         if (v < nvec) st_global_v4(dst + ((size_t)v << 4), buf[u]);
       }
     }
-    if (topk_w != nullptr && lane < g.K)
-      reinterpret_cast<float*>(pb + rg.comb_w)[(size_t)slot * g.K + lane] = topk_w[(size_t)i * g.K + lane];
+    // side values returned with the row: K floats per row in rank mode, one in expert mode
+    const int wk = g.mode == 0 ? g.K : 1;
+    if (topk_w != nullptr && lane < wk)
+      reinterpret_cast<float*>(pb + rg.comb_w)[(size_t)slot * wk + lane] = topk_w[(size_t)i * wk + lane];
   }
   if (last_block_arrive(block_counter, gridDim.x)) {
     if (threadIdx.x < g.R) {
@@ -191,11 +193,19 @@ combine_reduce_kernel(EpGeom g, EpRegions rg, char* self_base, const int* __rest
       }
       st_global_v4(out + (size_t)t * row_bytes + ((size_t)v << 4), Vec16<T>::pack(a));
     }
-    if (out_topk_w != nullptr && lane < g.K) {
-      float s = 0.f;
-      for (unsigned mm = vmask; mm; mm &= mm - 1)
-        s += comb_w[(size_t)s_slot[warp][__ffs(mm) - 1] * g.K + lane];
-      out_topk_w[(size_t)t * g.K + lane] = s;
+    if (out_topk_w != nullptr) {
+      if (g.mode == 0) {
+        // rank mode: [T,K] = sum over destination ranks of the K side values of each row
+        if (lane < g.K) {
+          float s = 0.f;
+          for (unsigned mm = vmask; mm; mm &= mm - 1)
+            s += comb_w[(size_t)s_slot[warp][__ffs(mm) - 1] * g.K + lane];
+          out_topk_w[(size_t)t * g.K + lane] = s;
+        }
+      } else if (lane < J) {
+        // expert mode: [T,K], entry k is the single side value returned for item (t,k)
+        out_topk_w[(size_t)t * J + lane] = slot >= 0 ? comb_w[slot] : 0.f;
+      }
     }
     __syncwarp();
   }

@@ -29,7 +29,8 @@ def main() -> int:
     group, ep_rank, _ = D.create_ep_group(args.ep)
     dev = torch.device("cuda", torch.cuda.current_device())
     T, H, E, K = args.num_local_tokens + 16 * ep_rank, args.token_hidden, args.num_of_experts, args.topk
-    cfg = Buffer.get_dispatch_config(args.ep, T + 16 * args.ep, K, E)
+    cfg = Buffer.get_dispatch_config(args.ep, args.num_local_tokens + 16 * args.ep, K, E,
+                                     group_by_expert=True)  # same on every rank
     buf = Buffer(group, cfg.get_nvl_buffer_size_hint(H * 2, args.ep), 0, timeout_s=10.0)
     oracle = AllToAllTokenDispatcher(group, E)
     ok = True
@@ -80,4 +81,4 @@ def main() -> int:
 
 
 if __name__ == "__main__":
-    sys.exit(main())
+    D.run_main(main)

@@ -1,0 +1,48 @@
+"""A Megatron-style MoE layer: router -> dispatch -> grouped experts -> combine.
+
+The reference's "model" is exactly this loop with a random router stand-in
+(`DeepEP_Megatron/test_deepep_moe_dispatch_combine.py:731-742,766-815`); here it is an
+`nn.Module` with a learnable router so that forward AND backward run (dispatch and combine
+are each other's backward, expert GEMMs have dgrad/wgrad).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from .experts import build_experts
+from .token_dispatcher import B200TokenDispatcher
+
+
+def topk_softmax_router(logits: torch.Tensor, topk: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(indices int64 [T,K], probabilities f32 [T,K] renormalised over the chosen experts)."""
+    probs = torch.softmax(logits.float(), dim=-1)
+    w, idx = torch.topk(probs, topk, dim=-1)
+    return idx, w / w.sum(-1, keepdim=True)
+
+
+class MoELayer(torch.nn.Module):
+    def __init__(self, hidden_size: int, ffn_hidden_size: int, num_experts: int, topk: int, group=None, *,
+                 ep_size: int = 1, ep_rank: int = 0, dtype=torch.bfloat16, activation: str = "swiglu",
+                 expert_backend: str = "auto", dispatcher_mode: str = "fused", world=None, device="cuda"):
+        super().__init__()
+        if num_experts % ep_size:
+            raise ValueError("num_experts must be divisible by the EP size")
+        self.hidden_size, self.num_experts, self.topk = hidden_size, num_experts, topk
+        self.num_local_experts = num_experts // ep_size
+        self.router = torch.nn.Linear(hidden_size, num_experts, bias=False, dtype=torch.float32, device=device)
+        torch.nn.init.normal_(self.router.weight, std=0.02)
+        self.experts, self.expert_backend = build_experts(expert_backend, self.num_local_experts, hidden_size,
+                                                          ffn_hidden_size, dtype, activation, device)
+        self.dispatcher = B200TokenDispatcher(group, self.num_local_experts, num_experts,
+                                              ep_rank * self.num_local_experts, mode=dispatcher_mode, world=world)
+
+    def forward(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """hidden_states [T,H]; router_logits [T,E] override the learnable router when given."""
+        if router_logits is None:
+            router_logits = self.router(hidden_states.float())
+        idx, probs = topk_softmax_router(router_logits, self.topk)
+        rows, tokens_per_expert, row_probs = self.dispatcher.dispatch(hidden_states, idx, probs)
+        out_rows = self.experts(rows, tokens_per_expert, row_probs)
+        return self.dispatcher.combine(out_rows)

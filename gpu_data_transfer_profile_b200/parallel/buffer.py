@@ -130,13 +130,15 @@ class Buffer:
 
     @staticmethod
     def get_dispatch_config(group_size: int, num_max_tokens_per_rank: int = 4096, num_topk: int = 8,
-                            num_experts: int = 256) -> Config:
-        return Config(Buffer.num_sms, num_max_tokens_per_rank, num_topk, num_experts)
+                            num_experts: int = 256, group_by_expert: bool = False) -> Config:
+        return Config(Buffer.num_sms, num_max_tokens_per_rank, num_topk, num_experts,
+                      group_by_expert=group_by_expert)
 
     @staticmethod
     def get_combine_config(group_size: int, num_max_tokens_per_rank: int = 4096, num_topk: int = 8,
-                           num_experts: int = 256) -> Config:
-        return Config(Buffer.num_sms, num_max_tokens_per_rank, num_topk, num_experts)
+                           num_experts: int = 256, group_by_expert: bool = False) -> Config:
+        return Config(Buffer.num_sms, num_max_tokens_per_rank, num_topk, num_experts,
+                      group_by_expert=group_by_expert)
 
     # ---- construction ----------------------------------------------------------------
     def __init__(self, group=None, num_nvl_bytes: int = 0, num_rdma_bytes: int = 0,
@@ -475,6 +477,10 @@ class Buffer:
                 config: Optional[Config] = None, previous_event=None, async_finish: bool = False,
                 allocate_on_comm_stream: bool = False, *, item_weights=None):
         """-> (combined_x[T,H], combined_topk_weights | None, event).
+        `topk_weights`: side values that travel back with the rows. Rank mode: [N_recv,K], summed
+        over the destination ranks into [T,K] (the gradient of the routing weights when combine is
+        dispatch's backward, `DeepEP_Megatron/test_deepep_moe_dispatch_combine.py:158-165`).
+        Expert mode: [N_recv] (one value per row), returned as [T,K].
         Unweighted sum over the rows that each token was sent to (an identity expert returns
         x times the number of destinations, `DeepEP_v1/deepep_v1_combine.py:335-342`);
         `item_weights[T,J]` (J = ranks in rank mode, top-k in expert mode) turns it into a

@@ -24,6 +24,7 @@ class Config:
     num_topk: int = 8
     num_experts: int = 256
     combine_elem_bytes: int = 2
+    group_by_expert: bool = False   # size for one row per (token, expert) instead of per (token, rank)
 
     def per_row_bytes(self, hidden_bytes: int) -> int:
         """Bytes that one receive row plus one combine slot occupy (all side arrays)."""
@@ -36,6 +37,9 @@ class Config:
 
     def get_nvl_buffer_size_hint(self, hidden_bytes: int, group_size: int) -> int:
         rows = group_size * self.num_max_tokens_per_rank
+        if self.group_by_expert:
+            # worst case: every token of every rank picks min(top-k, local experts) experts here
+            rows *= max(1, min(self.num_topk, max(self.num_experts // group_size, 1)))
         body = 2 * rows * self.per_row_bytes(hidden_bytes)  # two epoch parities
         return FIXED_BYTES + align_up(body, REGION_ALIGN) + 16 * REGION_ALIGN * 2
 

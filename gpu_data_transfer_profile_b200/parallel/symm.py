@@ -65,7 +65,12 @@ class ProcessWorld:
     def _map_peers(self, region: SymmetricRegion) -> List[int]:
         handle = region.C.ipc_export(region.local_ptr)
         handles = [None] * self.size
-        dist.all_gather_object(handles, handle, group=self.group)
+        dist.all_gather_object(handles, (handle, region.nbytes), group=self.group)
+        sizes = sorted({n for _, n in handles})
+        if len(sizes) != 1:
+            raise ValueError(f"symmetric region size differs across ranks: {sizes}; every rank must "
+                             "pass the same num_nvl_bytes")
+        handles = [h for h, _ in handles]
         out = []
         with torch.cuda.device(self.device):
             for i, h in enumerate(handles):

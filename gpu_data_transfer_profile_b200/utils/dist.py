@@ -107,3 +107,23 @@ def ordered_print(msg: str, group=None, file=sys.stdout) -> None:
 def shutdown() -> None:
     if is_dist():
         dist.destroy_process_group()
+
+
+def run_main(main) -> None:
+    """Run a CLI `main() -> int`; on any exception print it with the rank and leave the process
+    at once (exit code 1) so that the launcher tears the other ranks down instead of letting them
+    wait inside a collective. Parity: the top-level handler of `DeepEP_v1/deepep_v1_dispatch.py:384-394`."""
+    import traceback
+    try:
+        code = main()
+    except SystemExit as e:
+        code = e.code if isinstance(e.code, int) else 1
+    except BaseException:
+        sys.stdout.flush()
+        print(f"[rank {os.environ.get('RANK', '0')}] fatal:", file=sys.stderr)
+        traceback.print_exc()
+        sys.stderr.flush()
+        os._exit(1)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(int(code or 0))
