@@ -11,6 +11,7 @@
 #include "copy/ce_copy.h"
 #include "copy/copy_api.h"
 #include "ep/api.h"
+#include "ep/ll_api.h"
 
 namespace py = pybind11;
 using namespace b200ep;
@@ -134,6 +135,7 @@ void check_launch(const char* what) { cuda_ok(cudaGetLastError(), what); }
 
 #include "bindings_ep.inc"
 #include "bindings_copy.inc"
+#include "bindings_ll.inc"
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("MAX_RANKS") = kMaxRanks;
@@ -152,4 +154,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("view_tensor", &view_tensor);
   bind_ep(m);
   bind_copy(m);
+  bind_ll(m);
 }

@@ -6,7 +6,7 @@
 // `DeepEP_v1/deepep_v1_dispatch.py:212-230` and, in expert mode, also the multihot/permute
 // glue of `DeepEP_Megatron/test_deepep_moe_dispatch_combine.py:276-388`.
 #include <cuda_bf16.h>
-#include <cuda_fp8.h>
+#include "cast.cuh"
 #include "ep.cuh"
 #include "api.h"
 
@@ -14,15 +14,6 @@ namespace b200ep {
 
 constexpr int kSendWarps = 16;  // warps per CTA in the send kernels
 constexpr int kUnroll = 4;
-
-__device__ __forceinline__ float bf16lo(uint32_t u) { return __uint_as_float(u << 16); }
-__device__ __forceinline__ float bf16hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
-
-__device__ __forceinline__ uint32_t cvt4_e4m3(float a, float b, float c, float d) {
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-  return lo | (hi << 16);
-}
 
 template <int MODE, bool FP8, bool CACHED>
 __global__ void __launch_bounds__(kSendWarps * 32)
@@ -121,24 +112,8 @@ dispatch_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, EpMeta m,
           a = ld_global_nc_v4(src + (size_t)el * 2);
           b = ld_global_nc_v4(src + (size_t)el * 2 + 16);
         }
-        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        float f[16];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) { f[2 * q] = bf16lo(w[q]); f[2 * q + 1] = bf16hi(w[q]); }
-        float amax = 0.f;
-#pragma unroll
-        for (int q = 0; q < 16; ++q) amax = fmaxf(amax, fabsf(f[q]));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-        amax = fmaxf(amax, 1e-4f);
-        const float scale = amax * (1.f / 448.f);
-        const float inv = 448.f / amax;
-        uint4 o;
-        o.x = cvt4_e4m3(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
-        o.y = cvt4_e4m3(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
-        o.z = cvt4_e4m3(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
-        o.w = cvt4_e4m3(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+        float scale;
+        const uint4 o = cast_block_fp8(a, b, &scale);
         if (act) {
           for (unsigned mm = vmask; mm; mm &= mm - 1) {
             const int j = __ffs(mm) - 1;

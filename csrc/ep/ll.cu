@@ -1,0 +1,299 @@
+// Low-latency (decode) dispatch and combine.
+//
+// Not exercised by the reference scripts (they only drive DeepEP's normal mode); the call
+// shapes follow upstream DeepEP's `low_latency_dispatch` / `low_latency_combine`. Design:
+//  * fixed-capacity receive layout: region [local expert][source rank][M rows], so a sender
+//    needs no count exchange before it stores; one copy per (token, expert), fp8 e4m3 with
+//    1x128 scales (or bf16), each row carrying (token, k) so the result can be returned;
+//  * no host synchronisation and no host-side state per call: the call's epoch lives in device
+//    memory and is advanced by the kernel itself, regions are double-buffered by its parity,
+//    every kernel argument is constant -> the four kernels can be captured in a CUDA graph;
+//  * send and receive halves are separate launches (receive = bounded wait on the peers'
+//    flags, then local packing / weighted reduction), which also gives hook-style completion.
+#include <cuda_bf16.h>
+#include "cast.cuh"
+#include "ep.cuh"
+#include "ll_api.h"
+
+namespace b200ep {
+
+constexpr int kLLThreads = 256;  // 8 warps work on one row together
+
+__device__ __forceinline__ int block_epoch(const int* epoch_ptr, int add) {
+  __shared__ int s_epoch;
+  if (threadIdx.x == 0) s_epoch = *reinterpret_cast<const volatile int*>(epoch_ptr) + add;
+  __syncthreads();
+  return s_epoch;
+}
+
+// ---------------------------------------------------------------------------------------
+// dispatch, send half: one CTA per token at a time.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kLLThreads)
+ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
+                        const long long* __restrict__ topk_idx, int* send_cnt, int* epoch_ptr,
+                        unsigned int* block_counter, int* status) {
+  __shared__ char* s_dst[kMaxItemsPerToken];
+  __shared__ float* s_scl[kMaxItemsPerToken];
+  __shared__ int s_n;
+  const int epoch = block_epoch(epoch_ptr, 1);
+  const int par = epoch & 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kLLThreads / 32;
+  const int row_bytes = P.fp8 ? P.H : P.H * 2;
+  const int scale_cols = P.H / 128;
+  for (int t = blockIdx.x; t < P.T; t += gridDim.x) {
+    if (threadIdx.x == 0) s_n = 0;
+    __syncthreads();
+    if (threadIdx.x < P.K) {
+      const long long e = topk_idx[(size_t)t * P.K + threadIdx.x];
+      if (e >= 0 && e < P.E) {
+        const int slot = atomicAdd(&send_cnt[e], 1);
+        if (slot < P.M) {
+          const int d = (int)e / P.El, el = (int)e % P.El;
+          const size_t row = ((size_t)el * P.R + P.rank) * P.M + slot;
+          char* pb = peers.base[d];
+          reinterpret_cast<int*>(pb + P.recv_src[par])[row] = (t << 5) | (int)threadIdx.x;
+          const int i = atomicAdd(&s_n, 1);
+          s_dst[i] = pb + P.recv_x[par] + row * row_bytes;
+          s_scl[i] = reinterpret_cast<float*>(pb + P.recv_scales[par]) + row * scale_cols;
+        } else {
+          set_status(status, kOverflowRecv);
+        }
+      } else if (e != -1) {
+        set_status(status, kBadExpertIndex);
+      }
+    }
+    __syncthreads();
+    const int n = s_n;
+    const char* src = x + (size_t)t * P.H * 2;
+    if (P.fp8) {
+      const int nsteps = (P.H + 511) / 512;
+      for (int it = warp; it < nsteps; it += nwarps) {
+        const int el = it * 512 + lane * 16;
+        const bool act = el < P.H;
+        uint4 a = make_uint4(0, 0, 0, 0), b = a;
+        if (act) {
+          a = ld_global_nc_v4(src + (size_t)el * 2);
+          b = ld_global_nc_v4(src + (size_t)el * 2 + 16);
+        }
+        float scale;
+        const uint4 o = cast_block_fp8(a, b, &scale);
+        if (act) {
+          for (int j = 0; j < n; ++j) {
+            st_global_v4(s_dst[j] + el, o);
+            if ((lane & 7) == 0) s_scl[j][el >> 7] = scale;
+          }
+        }
+      }
+    } else {
+      const int nvec = (P.H * 2) >> 4;
+      for (int v = threadIdx.x; v < nvec; v += kLLThreads) {
+        const uint4 val = ld_global_nc_v4(src + ((size_t)v << 4));
+        for (int j = 0; j < n; ++j) st_global_v4(s_dst[j] + ((size_t)v << 4), val);
+      }
+    }
+    __syncthreads();
+  }
+  if (!last_block_arrive(block_counter, gridDim.x)) return;
+  // last CTA: publish my per-expert counts to the owners, reset them, raise the flags.
+  for (int e = threadIdx.x; e < P.E; e += kLLThreads) {
+    const int c = min(*reinterpret_cast<volatile int*>(&send_cnt[e]), P.M);
+    send_cnt[e] = 0;
+    int* dst = reinterpret_cast<int*>(peers.base[e / P.El] + P.count[par]) + (e % P.El) * P.R + P.rank;
+    st_relaxed_sys(dst, c);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < P.R) {
+    int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + P.flags) + kChLLDispatch * kMaxRanks + P.rank;
+    st_release_sys(flag, epoch);
+  }
+  if (threadIdx.x == 0) *epoch_ptr = epoch;
+}
+
+// ---------------------------------------------------------------------------------------
+// dispatch, receive half: wait for every source, then pack each local expert's rows
+// contiguously: out_x[el][0..count[el]) ordered by source rank.  grid = (El, split)
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kLLThreads)
+ll_dispatch_recv_kernel(LLParams P, char* self_base, char* __restrict__ out_x,
+                        float* __restrict__ out_scales, int* __restrict__ out_src,
+                        int* __restrict__ out_count, int2* __restrict__ out_range,
+                        const int* epoch_ptr, int* status) {
+  __shared__ int s_off[kMaxRanks + 1];
+  __shared__ int ok;
+  const int epoch = block_epoch(epoch_ptr, 0);
+  const int par = epoch & 1;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < P.R) {
+    const int* flags = reinterpret_cast<const int*>(self_base + P.flags) + kChLLDispatch * kMaxRanks;
+    if (!wait_flag_ge(flags + threadIdx.x, epoch, P.timeout_ns, status, kTimeoutLowLatency)) ok = 0;
+  }
+  __syncthreads();
+  const int el = blockIdx.x;
+  if (!ok) {
+    if (threadIdx.x == 0 && blockIdx.y == 0) out_count[el] = 0;
+    return;
+  }
+  const int* cnt = reinterpret_cast<const int*>(self_base + P.count[par]) + el * P.R;
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int s = 0; s < P.R; ++s) {
+      s_off[s] = acc;
+      int c = __ldcg(&cnt[s]);
+      c = c < 0 ? 0 : (c > P.M ? P.M : c);
+      if (blockIdx.y == 0) out_range[el * P.R + s] = make_int2(acc, c);
+      acc += c;
+    }
+    s_off[P.R] = acc;
+    if (blockIdx.y == 0) out_count[el] = acc;
+  }
+  __syncthreads();
+  const int total = s_off[P.R];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kLLThreads / 32;
+  const int row_bytes = P.fp8 ? P.H : P.H * 2;
+  const int scale_cols = P.H / 128;
+  const size_t cap = (size_t)P.R * P.M;
+  for (int j = blockIdx.y * nwarps + warp; j < total; j += gridDim.y * nwarps) {
+    int s = 0;
+    while (s + 1 < P.R && j >= s_off[s + 1]) ++s;
+    const size_t in_row = ((size_t)el * P.R + s) * P.M + (j - s_off[s]);
+    const size_t out_row = (size_t)el * cap + j;
+    const char* src = self_base + P.recv_x[par] + in_row * row_bytes;
+    char* dst = out_x + out_row * row_bytes;
+    for (int v = lane; v < (row_bytes >> 4); v += 32)
+      st_global_v4(dst + ((size_t)v << 4), ld_global_v4(src + ((size_t)v << 4)));
+    if (P.fp8) {
+      const float* ss = reinterpret_cast<const float*>(self_base + P.recv_scales[par]) + in_row * scale_cols;
+      for (int c = lane; c < scale_cols; c += 32) out_scales[out_row * scale_cols + c] = ss[c];
+    }
+    if (lane == 0) {
+      const int info = reinterpret_cast<const int*>(self_base + P.recv_src[par])[in_row];
+      out_src[out_row] = (s << 24) | (info & 0xffffff);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// combine, send half: row (el, j) goes back to its source's slot (token, k). grid = (El, split)
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kLLThreads)
+ll_combine_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
+                       const int* __restrict__ src_info, const int* __restrict__ count,
+                       int* epoch_ptr, unsigned int* block_counter, int* status) {
+  const int epoch = block_epoch(epoch_ptr, 1);
+  const int par = epoch & 1;
+  const int el = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kLLThreads / 32;
+  const size_t cap = (size_t)P.R * P.M;
+  int total = count[el];
+  total = total < 0 ? 0 : (total > (int)cap ? (int)cap : total);
+  const int row_bytes = P.H * 2;
+  for (int j = blockIdx.y * nwarps + warp; j < total; j += gridDim.y * nwarps) {
+    const int info = src_info[(size_t)el * cap + j];
+    const int s = (info >> 24) & 0xff, t = (info & 0xffffff) >> 5, k = info & 31;
+    if (s >= P.R || t >= P.M || k >= P.K) {
+      if (lane == 0) set_status(status, kOverflowSlots);
+      continue;
+    }
+    const char* src = x + ((size_t)el * cap + j) * row_bytes;
+    char* dst = peers.base[s] + P.comb_x[par] + ((size_t)t * P.K + k) * row_bytes;
+    for (int v0 = lane; v0 < (row_bytes >> 4); v0 += 128) {
+      uint4 buf[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + u * 32 < (row_bytes >> 4)) buf[u] = ld_global_nc_v4(src + ((size_t)(v0 + u * 32) << 4));
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + u * 32 < (row_bytes >> 4)) st_global_v4(dst + ((size_t)(v0 + u * 32) << 4), buf[u]);
+    }
+  }
+  if (!last_block_arrive(block_counter, gridDim.x * gridDim.y)) return;
+  if (threadIdx.x < P.R) {
+    int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + P.flags) + kChLLCombine * kMaxRanks + P.rank;
+    st_release_sys(flag, epoch);
+  }
+  if (threadIdx.x == 0) *epoch_ptr = epoch;
+}
+
+// combine, receive half: out[t] = sum_k w[t,k] * slot(t,k) over k with topk_idx[t,k] >= 0.
+__global__ void __launch_bounds__(kLLThreads)
+ll_combine_recv_kernel(LLParams P, char* self_base, const long long* __restrict__ topk_idx,
+                       const float* __restrict__ topk_w, char* __restrict__ out,
+                       const int* epoch_ptr, int* status) {
+  __shared__ float s_w[kMaxItemsPerToken];
+  __shared__ int ok;
+  const int epoch = block_epoch(epoch_ptr, 0);
+  const int par = epoch & 1;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < P.R) {
+    const int* flags = reinterpret_cast<const int*>(self_base + P.flags) + kChLLCombine * kMaxRanks;
+    if (!wait_flag_ge(flags + threadIdx.x, epoch, P.timeout_ns, status, kTimeoutLowLatency)) ok = 0;
+  }
+  __syncthreads();
+  if (!ok) return;
+  const int row_bytes = P.H * 2;
+  const int nvec = row_bytes >> 4;
+  for (int t = blockIdx.x; t < P.T; t += gridDim.x) {
+    if (threadIdx.x < P.K) {
+      const long long e = topk_idx[(size_t)t * P.K + threadIdx.x];
+      s_w[threadIdx.x] = (e >= 0 && e < P.E) ? (topk_w ? topk_w[(size_t)t * P.K + threadIdx.x] : 1.f) : 0.f;
+    }
+    __syncthreads();
+    const char* base = self_base + P.comb_x[par] + (size_t)t * P.K * row_bytes;
+    for (int v = threadIdx.x; v < nvec; v += kLLThreads) {
+      float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int k = 0; k < P.K; ++k) {
+        const float w = s_w[k];
+        if (w == 0.f) continue;
+        const uint4 val = ld_global_v4(base + (size_t)k * row_bytes + ((size_t)v << 4));
+        const uint32_t u[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { a[2 * q] += w * bf16lo(u[q]); a[2 * q + 1] += w * bf16hi(u[q]); }
+      }
+      uint4 o;
+      uint32_t* ou = &o.x;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a[2 * q], a[2 * q + 1]);
+        ou[q] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      st_global_v4(out + (size_t)t * row_bytes + ((size_t)v << 4), o);
+    }
+    __syncthreads();
+  }
+}
+
+// ---- launchers -------------------------------------------------------------------------
+void launch_ll_dispatch_send(const LLParams& P, const PeerPtrs& peers, const char* x,
+                             const long long* topk_idx, int* send_cnt, int* epoch_ptr,
+                             unsigned int* counter, int* status, int blocks, cudaStream_t st) {
+  int g = P.T < blocks ? P.T : blocks;
+  if (g < 1) g = 1;
+  ll_dispatch_send_kernel<<<g, kLLThreads, 0, st>>>(P, peers, x, topk_idx, send_cnt, epoch_ptr, counter, status);
+}
+void launch_ll_dispatch_recv(const LLParams& P, char* self_base, char* out_x, float* out_scales,
+                             int* out_src, int* out_count, int* out_range, const int* epoch_ptr,
+                             int* status, int split, cudaStream_t st) {
+  if (split < 1) split = 1;
+  ll_dispatch_recv_kernel<<<dim3(P.El, split), kLLThreads, 0, st>>>(
+      P, self_base, out_x, out_scales, out_src, out_count, reinterpret_cast<int2*>(out_range), epoch_ptr, status);
+}
+void launch_ll_combine_send(const LLParams& P, const PeerPtrs& peers, const char* x, const int* src_info,
+                            const int* count, int* epoch_ptr, unsigned int* counter, int* status,
+                            int split, cudaStream_t st) {
+  if (split < 1) split = 1;
+  ll_combine_send_kernel<<<dim3(P.El, split), kLLThreads, 0, st>>>(P, peers, x, src_info, count, epoch_ptr,
+                                                                   counter, status);
+}
+void launch_ll_combine_recv(const LLParams& P, char* self_base, const long long* topk_idx,
+                            const float* topk_w, char* out, const int* epoch_ptr, int* status,
+                            int blocks, cudaStream_t st) {
+  int g = P.T < blocks ? P.T : blocks;
+  if (g < 1) g = 1;
+  ll_combine_recv_kernel<<<g, kLLThreads, 0, st>>>(P, self_base, topk_idx, topk_w, out, epoch_ptr, status);
+}
+
+}  // namespace b200ep

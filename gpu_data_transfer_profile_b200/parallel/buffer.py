@@ -156,7 +156,7 @@ class Buffer:
         self.device = self.world.device
         self.timeout_s = float(timeout_s)
         self.blocks_per_sm = blocks_per_sm
-        if self.num_nvl_bytes < FIXED_BYTES * 2:
+        if self.num_nvl_bytes < FIXED_BYTES + REGION_ALIGN:
             raise ValueError("num_nvl_bytes too small; use Config.get_nvl_buffer_size_hint")
         self.region = SymmetricRegion(self.world, self.num_nvl_bytes)
         with torch.cuda.device(self.device):
@@ -205,8 +205,9 @@ class Buffer:
     def _get_carve(self, E: int, K: int, H: int, row_bytes: int, comb_row_bytes: int) -> _Carve:
         key = (E, K, H, row_bytes, comb_row_bytes)
         if self._carve is None or self._carve.key != key:
-            if self._carve is not None:
+            if self._carve is not None or self._ll is not None:
                 self.barrier()           # region reuse with another shape: drain every rank first
+            self._ll = None
             self._carve = _Carve(self.num_nvl_bytes, self.group_size, E, K, H, row_bytes, comb_row_bytes)
         return self._carve
 
@@ -219,6 +220,8 @@ class Buffer:
         if allocate_on_comm_stream and not async_finish:
             raise ValueError("allocate_on_comm_stream=True requires async_finish=True")
         compute = torch.cuda.current_stream(self.device)
+        if self.world.local:
+            self.comm_stream = compute       # virtual ranks share whatever stream is current
         if self.comm_stream != compute:
             if previous_event is not None and getattr(previous_event, "event", None) is not None:
                 ev = previous_event.event.event
@@ -493,3 +496,166 @@ class Buffer:
                 out = out + (bias[0] if isinstance(bias, (tuple, list)) else bias)
         ev = self._exit(compute, async_finish, [out, x] + ([out_w] if out_w is not None else []))
         return out, out_w, ev
+
+    # ---- low-latency mode -------------------------------------------------------------
+    @staticmethod
+    def get_low_latency_nvl_size_hint(num_max_dispatch_tokens_per_rank: int, hidden: int, num_ranks: int,
+                                      num_experts: int, num_topk: int = 8) -> int:
+        """Bytes of symmetric memory that low-latency mode needs for these bounds."""
+        return _LLCarve.required_bytes(num_ranks, num_experts, num_max_dispatch_tokens_per_rank, hidden, num_topk)
+
+    get_low_latency_rdma_size_hint = get_low_latency_nvl_size_hint   # upstream DeepEP's name
+
+    def clean_low_latency_buffer(self, num_max_dispatch_tokens_per_rank: int = 0, hidden: int = 0,
+                                 num_experts: int = 0) -> None:
+        """Nothing to clean: flags are epochs and regions are double-buffered."""
+
+    def _ll_state(self, E: int, K: int, H: int, M: int):
+        key = (E, K, H, M)
+        if self._ll is None or self._ll["key"] != key:
+            if self._ll is not None or self._carve is not None:
+                self.barrier()
+            carve = _LLCarve(self.num_nvl_bytes, self.group_size, E, M, H, K)
+            dev = self.device
+            self._ll = dict(key=key, carve=carve,
+                            epochs=torch.zeros(2, dtype=torch.int32, device=dev),
+                            send_cnt=torch.zeros(E, dtype=torch.int32, device=dev),
+                            counters=torch.zeros(2, dtype=torch.int32, device=dev))
+            self._carve = None
+        return self._ll
+
+    def _ll_params(self, st, T: int, fp8: bool):
+        E, K, H, M = st["key"]
+        c = st["carve"]
+        R = self.group_size
+        return [self.rank, R, E, E // R, K, H, M, T, int(fp8), 0, *c.count, *c.recv_x, *c.recv_scales,
+                *c.recv_src, *c.comb_x, self._timeout_ns()]
+
+    def _ll_dispatch_send(self, x, topk_idx, M, E, use_fp8):
+        if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
+            raise ValueError("low-latency dispatch takes a contiguous bf16 [tokens, hidden] tensor")
+        T, H = x.shape
+        if T > M:
+            raise ValueError(f"{T} tokens exceed num_max_dispatch_tokens_per_rank={M}")
+        if E % self.group_size:
+            raise ValueError("num_experts must be divisible by the group size")
+        topk_idx = topk_idx.to(torch.int64).contiguous()
+        K = topk_idx.shape[1]
+        st = self._ll_state(E, K, H, M)
+        pv = self._ll_params(st, T, use_fp8)
+        self.C.ll_dispatch_send(pv, self.peers, x, topk_idx, st["send_cnt"], st["epochs"][0:1],
+                                st["counters"][0:1], self.status_ptr, max(Buffer.num_sms * 4, 1))
+        return dict(st=st, pv=pv, T=T, H=H, K=K, E=E, M=M, fp8=use_fp8, topk_idx=topk_idx, x=x)
+
+    def _ll_dispatch_recv(self, d):
+        R, El, M, H = self.group_size, d["E"] // self.group_size, d["M"], d["H"]
+        dev = self.device
+        rows = R * M
+        if d["fp8"]:
+            out_x = torch.empty((El, rows, H), dtype=torch.float8_e4m3fn, device=dev)
+            out_s = torch.empty((El, rows, H // 128), dtype=torch.float32, device=dev)
+        else:
+            out_x = torch.empty((El, rows, H), dtype=torch.bfloat16, device=dev)
+            out_s = None
+        out_src = torch.empty((El, rows), dtype=torch.int32, device=dev)
+        out_count = torch.empty((El,), dtype=torch.int32, device=dev)
+        out_range = torch.empty((El, R, 2), dtype=torch.int32, device=dev)
+        self.C.ll_dispatch_recv(d["pv"], self.region.local_ptr, out_x, out_s, out_src, out_count, out_range,
+                                d["st"]["epochs"][0:1], self.status_ptr, 4)
+        handle = (out_src, out_range, M, H, d["E"], out_count, d["K"])
+        return ((out_x, out_s) if d["fp8"] else out_x), out_count, handle
+
+    def low_latency_dispatch(self, x, topk_idx, num_max_dispatch_tokens_per_rank: int, num_experts: int,
+                             use_fp8: bool = True, async_finish: bool = False,
+                             return_recv_hook: bool = False):
+        """-> (recv_x [E_local, R*M, H] | (fp8, scales), recv_count [E_local] i32, handle, event, hook).
+        The first recv_count[e] rows of expert e are valid. No host synchronisation; may be
+        captured in a CUDA graph. With return_recv_hook=True only the send half is launched and
+        the returned hook launches the receive half (then fills the same tensors)."""
+        compute = self._enter(None, False, False)
+        with torch.cuda.stream(self.comm_stream):
+            d = self._ll_dispatch_send(x, topk_idx, num_max_dispatch_tokens_per_rank, num_experts, use_fp8)
+            if return_recv_hook:
+                box = {}
+
+                def hook():
+                    with torch.cuda.stream(self.comm_stream):
+                        box["out"] = self._ll_dispatch_recv(d)
+                    return box["out"]
+                ev = self._exit(compute, async_finish, [x])
+                return None, None, None, ev, hook
+            recv_x, count, handle = self._ll_dispatch_recv(d)
+        flat = list(recv_x) if isinstance(recv_x, tuple) else [recv_x]
+        ev = self._exit(compute, async_finish, flat + [count, x])
+        return recv_x, count, handle, ev, None
+
+    def _ll_combine_send(self, x, handle):
+        src_info, _range, M, H, E, count, K = handle
+        st = self._ll_state(E, K, H, M)
+        if x.dtype != torch.bfloat16 or not x.is_contiguous():
+            raise ValueError("low-latency combine takes a contiguous bf16 [E_local, R*M, hidden] tensor")
+        pv = self._ll_params(st, 0, False)
+        self.C.ll_combine_send(pv, self.peers, x, src_info, count, st["epochs"][1:2], st["counters"][1:2],
+                               self.status_ptr, 8)
+        return dict(st=st, H=H)
+
+    def _ll_combine_recv(self, c, topk_idx, topk_weights, out=None):
+        topk_idx = topk_idx.to(torch.int64).contiguous()
+        T = topk_idx.shape[0]
+        pv = self._ll_params(c["st"], T, False)
+        if out is None:
+            out = torch.empty((T, c["H"]), dtype=torch.bfloat16, device=self.device)
+        w = topk_weights.to(torch.float32).contiguous() if topk_weights is not None else None
+        self.C.ll_combine_recv(pv, self.region.local_ptr, topk_idx, w, out, c["st"]["epochs"][1:2],
+                               self.status_ptr, max(Buffer.num_sms * 4, 1))
+        return out
+
+    def low_latency_combine(self, x, topk_idx, topk_weights, handle, async_finish: bool = False,
+                            return_recv_hook: bool = False, out: Optional[torch.Tensor] = None):
+        """-> (combined_x [T,H] bf16 = sum_k topk_weights[t,k] * expert output of (t,k), event, hook)."""
+        compute = self._enter(None, False, False)
+        with torch.cuda.stream(self.comm_stream):
+            c = self._ll_combine_send(x, handle)
+            if return_recv_hook:
+                def hook():
+                    with torch.cuda.stream(self.comm_stream):
+                        return self._ll_combine_recv(c, topk_idx, topk_weights, out)
+                return None, self._exit(compute, async_finish, [x]), hook
+            res = self._ll_combine_recv(c, topk_idx, topk_weights, out)
+        return res, self._exit(compute, async_finish, [res, x]), None
+
+
+class _LLCarve:
+    """Region offsets of low-latency mode (both epoch parities)."""
+
+    @staticmethod
+    def _sizes(R, E, M, H, K):
+        El = E // R
+        rows = El * R * M
+        return dict(recv_x=rows * H * 2, recv_scales=rows * max(H // 128, 1) * 4, recv_src=rows * 4,
+                    comb_x=M * K * H * 2)
+
+    @staticmethod
+    def required_bytes(R, E, M, H, K) -> int:
+        s = _LLCarve._sizes(R, E, M, H, K)
+        return FIXED_BYTES + 2 * sum(align_up(v, REGION_ALIGN) for v in s.values()) + REGION_ALIGN
+
+    def __init__(self, nbytes: int, R: int, E: int, M: int, H: int, K: int):
+        need = self.required_bytes(R, E, M, H, K)
+        if nbytes < need:
+            raise ValueError(f"buffer of {nbytes} bytes is too small for low-latency mode: need {need} "
+                             "(Buffer.get_low_latency_nvl_size_hint)")
+        El = E // R
+        csz = align_up(El * R * 4, REGION_ALIGN)
+        base = FIXED_BYTES // 2
+        if base + 2 * csz > FIXED_BYTES:
+            raise ValueError("too many experts for the low-latency control area")
+        self.count = (base, base + csz)
+        off = FIXED_BYTES
+        names = self._sizes(R, E, M, H, K)
+        for name in names:
+            setattr(self, name, [0, 0])
+        for p in range(2):
+            for name, sz in names.items():
+                getattr(self, name)[p] = off
+                off = align_up(off + sz, REGION_ALIGN)

@@ -46,6 +46,15 @@ class LocalGroup:
         return [b._combine_p2(sts[r], handles[r], item_weights[r] if item_weights is not None else None)
                 for r, b in enumerate(self.buffers)]
 
+    def low_latency_dispatch(self, xs, topk_idx, num_max_tokens: int, num_experts: int, use_fp8=True):
+        ds = [b._ll_dispatch_send(xs[r], topk_idx[r], num_max_tokens, num_experts, use_fp8)
+              for r, b in enumerate(self.buffers)]
+        return [b._ll_dispatch_recv(ds[r]) for r, b in enumerate(self.buffers)]
+
+    def low_latency_combine(self, ys, topk_idx, topk_weights, handles):
+        cs = [b._ll_combine_send(ys[r], handles[r]) for r, b in enumerate(self.buffers)]
+        return [b._ll_combine_recv(cs[r], topk_idx[r], topk_weights[r]) for r, b in enumerate(self.buffers)]
+
     def check_status(self):
         for b in self.buffers:
             b.check_status()
