@@ -12,6 +12,7 @@
 #include "copy/copy_api.h"
 #include "ep/api.h"
 #include "ep/ll_api.h"
+#include "gemm/gemm_api.h"
 
 namespace py = pybind11;
 using namespace b200ep;
@@ -136,6 +137,7 @@ void check_launch(const char* what) { cuda_ok(cudaGetLastError(), what); }
 #include "bindings_ep.inc"
 #include "bindings_copy.inc"
 #include "bindings_ll.inc"
+#include "bindings_gemm.inc"
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("MAX_RANKS") = kMaxRanks;
@@ -155,4 +157,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   bind_ep(m);
   bind_copy(m);
   bind_ll(m);
+  bind_gemm(m);
 }

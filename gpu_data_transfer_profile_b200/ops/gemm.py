@@ -1,0 +1,57 @@
+"""Python front-end of the tcgen05 grouped GEMM (csrc/gemm/grouped_gemm.cu).
+
+`expert_off` is a DEVICE int32 tensor [E_local+1] (exclusive prefix of rows per local expert),
+so no host synchronisation is needed to schedule tiles; the reference reads the split sizes
+back to the host for every call (`DeepEP_Megatron/test_deepep_moe_dispatch_combine.py:536,586`).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _ext
+
+PLAIN, SWIGLU, COMBINE = 0, 1, 2
+
+
+def _ctas(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def offsets_from_counts(tokens_per_expert, device) -> torch.Tensor:
+    t = torch.as_tensor(tokens_per_expert, dtype=torch.int64)
+    off = torch.zeros(t.numel() + 1, dtype=torch.int32)
+    off[1:] = torch.cumsum(t, 0).to(torch.int32)
+    return off.to(device, non_blocking=True)
+
+
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, expert_off: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+                 ctas: int = 0) -> torch.Tensor:
+    """out[r] = a[r] @ w[e(r)].T   (a bf16 [rows,K], w bf16 [E,N,K]) -> bf16 [rows,N]"""
+    if out is None:
+        out = torch.empty((a.shape[0], w.shape[1]), dtype=torch.bfloat16, device=a.device)
+    _ext.load().grouped_gemm(a, w, expert_off, PLAIN, out, None, None, [], 0, 0, 0, -1, 0, None, 0,
+                             ctas or _ctas(a.device))
+    return out
+
+
+def grouped_gemm_swiglu(a: torch.Tensor, w: torch.Tensor, expert_off: torch.Tensor, row_prob: Optional[torch.Tensor],
+                        *, out: Optional[torch.Tensor] = None, ctas: int = 0) -> torch.Tensor:
+    """w bf16 [E, 2F, K] (gate rows first): out[r] = silu(a[r] @ Wg.T) * (a[r] @ Wl.T) * row_prob[r] -> bf16 [rows,F]"""
+    F = w.shape[1] // 2
+    if out is None:
+        out = torch.empty((a.shape[0], F), dtype=torch.bfloat16, device=a.device)
+    _ext.load().grouped_gemm(a, w, expert_off, SWIGLU, out, row_prob, None, [], 0, 0, 0, -1, 0, None, 0,
+                             ctas or _ctas(a.device))
+    return out
+
+
+def grouped_gemm_combine(a: torch.Tensor, w: torch.Tensor, expert_off: torch.Tensor, recv_meta: torch.Tensor,
+                         peers, comb_off: int, slot_cap: int, rank: int, *, signal_flag_off: int = -1,
+                         epoch: int = 0, counter: Optional[torch.Tensor] = None, status_ptr: int = 0,
+                         ctas: int = 0) -> None:
+    """fc2 with the combine send fused into the epilogue: row r of a @ w[e].T is stored into slot
+    recv_meta[r,0] of rank recv_meta[r,1]'s combine region (peer LSU stores)."""
+    _ext.load().grouped_gemm(a, w, expert_off, COMBINE, None, None, recv_meta, list(peers), comb_off, slot_cap,
+                             rank, signal_flag_off, epoch, counter, status_ptr, ctas or _ctas(a.device))
