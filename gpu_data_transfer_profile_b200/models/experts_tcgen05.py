@@ -1,0 +1,92 @@
+"""Grouped expert MLP on this library's tcgen05 kernels.
+
+Forward: fc1 with SwiGLU x probability fused into its epilogue (one kernel), fc2 either as a
+plain grouped GEMM or with the combine send fused into its epilogue (`forward_fused_combine`).
+Tile scheduling reads the per-expert row offsets on the device. Backward runs the same math with
+library GEMMs through PyTorch (dgrad/wgrad kernels of this library are future work).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from ..ops import gemm as G
+from .experts import GroupedExpertsBase, activate
+
+
+def _mlp_backward(x, w1, w2, probs, counts, dy, gated, activation):
+    """Per-expert backward of y = fc2(act(fc1(x)) * p). Returns (dx, dw1, dw2, dprobs)."""
+    dx = torch.empty_like(x)
+    dw1, dw2 = torch.zeros_like(w1), torch.zeros_like(w2)
+    dp = torch.zeros_like(probs)
+    r = 0
+    for e, c in enumerate(counts):
+        if c == 0:
+            continue
+        sl = slice(r, r + c)
+        with torch.enable_grad():
+            xe = x[sl].detach().requires_grad_(True)
+            w1e, w2e = w1[e].detach().requires_grad_(True), w2[e].detach().requires_grad_(True)
+            pe = probs[sl].detach().requires_grad_(True)
+            a = activate(F.linear(xe, w1e), activation)
+            y = F.linear((a * pe[:, None]).to(xe.dtype), w2e)
+        gx, g1, g2, gp = torch.autograd.grad(y, [xe, w1e, w2e, pe], dy[sl])
+        dx[sl], dw1[e], dw2[e], dp[sl] = gx, g1, g2, gp
+        r += c
+    return dx, dw1, dw2, dp
+
+
+class _GroupedMLP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w1, w2, probs, expert_off, counts, activation):
+        if activation == "swiglu":
+            act = G.grouped_gemm_swiglu(x, w1, expert_off, probs)
+        else:
+            h = G.grouped_gemm(x, w1, expert_off)
+            act = (activate(h, activation) * probs[:, None]).to(x.dtype)
+        y = G.grouped_gemm(act, w2, expert_off)
+        ctx.save_for_backward(x, w1, w2, probs)
+        ctx.counts, ctx.activation = counts, activation
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w1, w2, probs = ctx.saved_tensors
+        dx, dw1, dw2, dp = _mlp_backward(x, w1, w2, probs, ctx.counts, dy.contiguous(), True, ctx.activation)
+        return dx, dw1, dw2, dp, None, None, None
+
+
+class Tcgen05GroupedExperts(GroupedExpertsBase):
+    def __init__(self, num_local_experts, hidden_size, ffn_hidden_size, dtype=torch.bfloat16,
+                 activation="swiglu", device="cuda", init_std: float = 0.02):
+        if dtype != torch.bfloat16:
+            raise ValueError("the tcgen05 grouped GEMM takes bf16 operands")
+        if hidden_size % 8 or ffn_hidden_size % 8 or (activation == "swiglu" and ffn_hidden_size % 128):
+            raise ValueError("hidden/ffn sizes must be multiples of 8 (ffn of 128 with swiglu)")
+        super().__init__(num_local_experts, hidden_size, ffn_hidden_size, dtype, activation, device, init_std)
+
+    @staticmethod
+    def _offsets(tokens_per_expert, device, expert_off=None):
+        counts = [int(v) for v in (tokens_per_expert.tolist() if torch.is_tensor(tokens_per_expert) else tokens_per_expert)]
+        if expert_off is None:
+            expert_off = G.offsets_from_counts(counts, device)
+        return counts, expert_off
+
+    def forward(self, hidden_states, tokens_per_expert, routed_probs, expert_off=None):
+        counts, off = self._offsets(tokens_per_expert, hidden_states.device, expert_off)
+        return _GroupedMLP.apply(hidden_states.contiguous(), self.weight1, self.weight2,
+                                 routed_probs.float().contiguous(), off, counts, self.activation)
+
+    @torch.no_grad()
+    def forward_fused_combine(self, hidden_states, routed_probs, buffer, handle):
+        """Inference/forward-only fast path: fc1(+SwiGLU x prob) then fc2 with the combine send in
+        its epilogue; returns the combined [T, H] tensor of THIS rank's tokens."""
+        El = self.num_local_experts
+        off = handle.meta[2 + El: 2 + El + El + 1]
+        x = hidden_states.contiguous()
+        if self.activation == "swiglu":
+            act = G.grouped_gemm_swiglu(x, self.weight1, off, routed_probs.float().contiguous())
+        else:
+            act = (activate(G.grouped_gemm(x, self.weight1, off), self.activation)
+                   * routed_probs.float()[:, None]).to(x.dtype)
+        return buffer.fused_fc2_combine(act, self.weight2, handle)

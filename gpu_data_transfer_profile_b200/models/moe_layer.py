@@ -25,11 +25,13 @@ def topk_softmax_router(logits: torch.Tensor, topk: int) -> Tuple[torch.Tensor, 
 class MoELayer(torch.nn.Module):
     def __init__(self, hidden_size: int, ffn_hidden_size: int, num_experts: int, topk: int, group=None, *,
                  ep_size: int = 1, ep_rank: int = 0, dtype=torch.bfloat16, activation: str = "swiglu",
-                 expert_backend: str = "auto", dispatcher_mode: str = "fused", world=None, device="cuda"):
+                 expert_backend: str = "auto", dispatcher_mode: str = "fused", world=None, device="cuda",
+                 fuse_combine: bool = True):
         super().__init__()
         if num_experts % ep_size:
             raise ValueError("num_experts must be divisible by the EP size")
         self.hidden_size, self.num_experts, self.topk = hidden_size, num_experts, topk
+        self.fuse_combine = fuse_combine
         self.num_local_experts = num_experts // ep_size
         self.router = torch.nn.Linear(hidden_size, num_experts, bias=False, dtype=torch.float32, device=device)
         torch.nn.init.normal_(self.router.weight, std=0.02)
@@ -44,5 +46,13 @@ class MoELayer(torch.nn.Module):
             router_logits = self.router(hidden_states.float())
         idx, probs = topk_softmax_router(router_logits, self.topk)
         rows, tokens_per_expert, row_probs = self.dispatcher.dispatch(hidden_states, idx, probs)
+        if (self.fuse_combine and not torch.is_grad_enabled() and self.dispatcher.mode == "fused"
+                and hasattr(self.experts, "forward_fused_combine")):
+            # forward-only fast path: the fc2 epilogue stores straight into the source ranks' slots
+            from . import fused_a2a as A
+            buf = A.get_buffer(self.dispatcher.group, A.get_hidden_bytes(hidden_states), self.dispatcher.world)
+            handle = self.dispatcher.handle
+            self.dispatcher.handle = None
+            return self.experts.forward_fused_combine(rows, row_probs, buf, handle)
         out_rows = self.experts(rows, tokens_per_expert, row_probs)
         return self.dispatcher.combine(out_rows)

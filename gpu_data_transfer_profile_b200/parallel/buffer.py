@@ -659,3 +659,40 @@ class _LLCarve:
             for name, sz in names.items():
                 getattr(self, name)[p] = off
                 off = align_up(off + sz, REGION_ALIGN)
+
+
+def _fused_fc2_combine(self: Buffer, act: torch.Tensor, w2: torch.Tensor, handle: DispatchHandle,
+                       item_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fc2 grouped GEMM whose epilogue IS the combine send: each output tile row is stored
+    straight into its token's slot on the source rank (peer LSU stores from the tensor-core
+    kernel), the last CTA raises the combine flags, and the source reduces on arrival.
+    act: bf16 [N_recv, F] rows grouped by local expert (expert-mode handle), w2: bf16 [E_local, H, F].
+    Returns combined [T, H] bf16."""
+    from ..ops import gemm as G
+    if handle.mode != 1:
+        raise ValueError("fused fc2+combine needs an expert-grouped dispatch handle")
+    carve = self._carve
+    if carve is None or carve.key[:3] != (handle.E, handle.K, handle.H):
+        raise ValueError("fused combine must follow a dispatch of the same shape on this buffer")
+    if w2.shape[1] != handle.H or act.dtype != torch.bfloat16:
+        raise ValueError("w2 must be [E_local, hidden, ffn] and act bf16")
+    compute = self._enter(None, False, False)
+    with torch.cuda.stream(self.comm_stream):
+        self._epoch["combine"] += 1
+        ep = self._epoch["combine"]
+        regions = carve.region_list(0, 0, ep & 1)
+        El = handle.E // self.group_size
+        expert_off = handle.meta[2 + El: 2 + El + El + 1]
+        flag_row = self.C.MAX_RANKS * 4 * 2          # byte offset of the combine channel's flag row
+        G.grouped_gemm_combine(act, w2, expert_off, handle.recv_meta, self.peers, regions[8], carve.slot_cap,
+                               self.rank, signal_flag_off=flag_row, epoch=ep, counter=self.counters[3:4],
+                               status_ptr=self.status_ptr)
+        geom = self._geom(E=handle.E, K=handle.K, T=handle.T, mode=1, H=handle.H, cap=handle.n_recv,
+                          slot_cap=carve.slot_cap, epoch=ep)
+        st = dict(ep=ep, regions=regions, geom=geom, dtype=torch.bfloat16, with_w=False)
+        out, _ = self._combine_p2(st, handle, item_weights)
+    self._exit(compute, False, [out, act])
+    return out
+
+
+Buffer.fused_fc2_combine = _fused_fc2_combine

@@ -45,3 +45,35 @@ def test_moe_layer_forward_backward_matches_dense_oracle(mode, activation):
         torch.testing.assert_close(gw1, rw1, atol=2e-4, rtol=2e-3)
     finally:
         A.release_buffers()
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_moe_layer_tcgen05_experts_bf16(fused):
+    """bf16 layer on the tcgen05 grouped GEMMs (separate combine with autograd, and the forward-only
+    path whose fc2 epilogue performs the combine send) against the fp32 dense oracle."""
+    from gpu_data_transfer_profile_b200.models import fused_a2a as A
+    from gpu_data_transfer_profile_b200.models.moe_layer import MoELayer
+    from gpu_data_transfer_profile_b200.parallel.symm import LocalWorld
+    torch.manual_seed(0)
+    T, H, F, E, K = 300, 512, 1024, 4, 2
+    world = LocalWorld.make(1)[0]
+    A.configure_buffer(num_max_tokens_per_rank=512, num_topk=K, num_experts=E, group_by_expert=True)
+    try:
+        layer = MoELayer(H, F, E, K, None, dtype=torch.bfloat16, activation="swiglu", expert_backend="tcgen05",
+                         dispatcher_mode="fused", world=world)
+        assert layer.expert_backend == "tcgen05_grouped_gemm"
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16).requires_grad_(not fused)
+        logits = torch.randn(T, E, device="cuda")
+        ref = _dense_oracle(x.detach().float(), logits, layer.experts.weight1.detach(), layer.experts.weight2.detach(),
+                            K, "swiglu")
+        if fused:
+            with torch.no_grad():
+                out = layer(x, logits)
+        else:
+            out = layer(x, logits)
+            out.float().sum().backward()
+            assert x.grad is not None and torch.isfinite(x.grad).all()
+            assert layer.experts.weight1.grad is not None and torch.isfinite(layer.experts.weight1.grad).all()
+        torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=5e-2)
+    finally:
+        A.release_buffers()
