@@ -104,3 +104,15 @@ def test_fill_values_stay_below_sentinels():
             assert P.layout_chunk_value(r, c) < P.SRC_GAP_SENTINEL
             assert P.msrc_chunk_value(r, c, c % 7) < P.SRC_GAP_SENTINEL
     assert P.pair_fill_value(3) != P.pair_prefill_value(3)
+
+
+def test_variant_selector_uses_nearest_measured_size():
+    from gpu_data_transfer_profile_b200.ops import variants as V
+    table = {"one-to-one": [{"nbytes": 4096, "variant": "lsu16"}, {"nbytes": 1 << 20, "variant": "tma_staged"},
+                            {"nbytes": 1 << 30, "variant": "ce"}]}
+    assert V.select("one-to-one", 8192, table) == "lsu16"
+    assert V.select("one-to-one", 3 << 20, table) == "tma_staged"
+    assert V.select("one-to-one", 1 << 29, table) == "ce"
+    with pytest.raises(KeyError):
+        V.select("ring-of-fire", 1, table)
+    assert V.select("round-robin", 1 << 20) in ("lsu_rr", "tma_rr", "ce_graph")
