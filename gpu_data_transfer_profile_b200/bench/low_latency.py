@@ -1,0 +1,94 @@
+"""Low-latency (decode) dispatch + combine: latency per call, eager and under a CUDA graph.
+
+Config of record: 128 tokens/rank, hidden 7168, 256 experts, top-8, fp8 e4m3 dispatch with
+1x128 scales, bf16 combine, seeded uniform top-8 selection. The reference has no low-latency
+path; the call shapes follow upstream DeepEP's `low_latency_dispatch` / `low_latency_combine`.
+
+    torchrun --nproc-per-node 8 -m gpu_data_transfer_profile_b200.bench.low_latency --ep 8
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from ..parallel.buffer import Buffer
+from ..parallel.symm import LocalWorld
+from ..ref.cpu_oracle import make_routing
+from ..utils import dist as D
+from . import ep_common as C
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--num-local-tokens", type=int, default=128)
+    ap.add_argument("--token-hidden", type=int, default=7168)
+    ap.add_argument("--num-of-experts", type=int, default=256)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--ep", type=int, required=True)
+    ap.add_argument("--num-max-dispatch-tokens-per-rank", type=int, default=0)
+    ap.add_argument("--no-fp8", action="store_true")
+    ap.add_argument("--warmup-iters", type=int, default=10)
+    ap.add_argument("--benchmark-iters", type=int, default=100)
+    ap.add_argument("--num-sms", type=int, default=32)
+    ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--jsonl", default=None)
+    a = ap.parse_args()
+    rank, world, _ = D.init_distributed()
+    group, ep_rank, _ = D.create_ep_group(a.ep)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    T, H, E, K = a.num_local_tokens, a.token_hidden, a.num_of_experts, a.topk
+    M = a.num_max_dispatch_tokens_per_rank or T
+    fp8 = not a.no_fp8
+    Buffer.set_num_sms(a.num_sms)
+    lw = None if D.is_dist() else LocalWorld.make(1, dev)[0]
+    buf = Buffer(group, Buffer.get_low_latency_nvl_size_hint(M, H, a.ep, E, K), 0, low_latency_mode=True, world=lw)
+    x = torch.randn(T, H, generator=torch.Generator().manual_seed(a.seed + rank)).to(torch.bfloat16).to(dev)
+    idx, w = make_routing(T, E, K, seed=a.seed * 7 + rank)
+    idx, w = idx.to(dev), w.to(dev)
+    out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+    El = E // a.ep
+
+    def step():
+        recv, count, handle, _, _ = buf.low_latency_dispatch(x, idx, M, E, use_fp8=fp8)
+        if fp8:   # identity "expert": dequantise (a real expert GEMM would consume fp8 + scales)
+            q, sc = recv
+            y = (q.float().view(El, -1, H // 128, 128) * sc[..., None]).view(El, -1, H).to(torch.bfloat16)
+        else:
+            y = recv
+        buf.low_latency_combine(y, idx, w, handle, out=out)
+
+    eager = C.timed_loop(step, a.warmup_iters, a.benchmark_iters, before=buf.barrier, group=group)
+    # the same step captured once and replayed: no host work per call
+    torch.cuda.synchronize()
+    D.barrier(group)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    graphed = C.timed_loop(graph.replay, a.warmup_iters, a.benchmark_iters, before=buf.barrier, group=group)
+    buf.check_status()
+    tol = 0.6 if fp8 else 0.08
+    ok = torch.allclose(out.float(), x.float() * w.sum(1, keepdim=True), atol=tol, rtol=0.08)
+    send_d = T * K * ((H + H // 128 * 4) if fp8 else H * 2)
+    send_c = T * K * H * 2
+    D.ordered_print(f"[rank {rank}] low-latency dispatch+combine eager={eager['mean_ms'] * 1e3:.1f} us "
+                    f"graph={graphed['mean_ms'] * 1e3:.1f} us (min {graphed['min_ms'] * 1e3:.1f} us) check={'OK' if ok else 'FAIL'}")
+    all_ok = D.all_ranks_boolean(ok)
+    C.emit(rank, dict(bench="low_latency", ep=a.ep, tokens=T, hidden=H, experts=E, topk=K, fp8=fp8,
+                      eager_us_max_over_ranks=eager["max_over_ranks_ms"] * 1e3,
+                      graph_us_max_over_ranks=graphed["max_over_ranks_ms"] * 1e3,
+                      bytes_dispatch=send_d, bytes_combine=send_c, includes="identity expert dequant between the halves",
+                      check=bool(all_ok)), a.jsonl)
+    buf.destroy()
+    D.shutdown()
+    return 0 if all_ok else 2
+
+
+if __name__ == "__main__":
+    D.run_main(main)
