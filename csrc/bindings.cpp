@@ -68,6 +68,12 @@ int64_t host_mapped_alloc(int64_t bytes) {
 }
 void host_mapped_free(int64_t p) { cudaFreeHost(ptr<void>(p)); cudaGetLastError(); }
 int host_read_i32(int64_t p, int64_t idx) { return reinterpret_cast<volatile int*>(ptr<int>(p))[idx]; }
+std::vector<int> host_read_i32_list(int64_t p, int64_t start, int64_t n) {
+  volatile int* w = reinterpret_cast<volatile int*>(ptr<int>(p)) + start;
+  std::vector<int> out((size_t)n);
+  for (int64_t i = 0; i < n; ++i) out[(size_t)i] = w[i];
+  return out;
+}
 void host_write_i32(int64_t p, int64_t idx, int v) { reinterpret_cast<volatile int*>(ptr<int>(p))[idx] = v; }
 // Spin on a pinned word until it reaches `want` (GIL released). Returns false on time-out.
 bool host_wait_ge(int64_t p, int64_t idx, int want, double timeout_s) {
@@ -152,6 +158,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("host_mapped_free", &host_mapped_free);
   m.def("host_read_i32", &host_read_i32);
   m.def("host_write_i32", &host_write_i32);
+  m.def("host_read_i32_list", &host_read_i32_list);
   m.def("host_wait_ge", &host_wait_ge);
   m.def("view_tensor", &view_tensor);
   bind_ep(m);

@@ -51,8 +51,12 @@ __global__ void layout_kernel(const long long* __restrict__ topk_idx, int T, int
 
 void launch_layout(const long long* topk_idx, int T, int K, int E, int R, int* per_rank,
                    int* per_expert, bool* in_rank, int* status, cudaStream_t st) {
-  cudaMemsetAsync(per_rank, 0, sizeof(int) * R, st);
-  cudaMemsetAsync(per_expert, 0, sizeof(int) * E, st);
+  if (per_expert == per_rank + R) {
+    cudaMemsetAsync(per_rank, 0, sizeof(int) * (R + E), st);   // one buffer: [R rank counts | E expert counts]
+  } else {
+    cudaMemsetAsync(per_rank, 0, sizeof(int) * R, st);
+    cudaMemsetAsync(per_expert, 0, sizeof(int) * E, st);
+  }
   if (T == 0) return;
   const int threads = 256;
   layout_kernel<<<(T + threads - 1) / threads, threads, (E + R) * sizeof(int), st>>>(

@@ -12,7 +12,7 @@ with a steady clock around submit + stream synchronise; the slowest rank defines
 The best variant per (pattern, size) is written as a selector table that `ops/variants.py` loads.
 
     torchrun --nproc-per-node 8 -m gpu_data_transfer_profile_b200.bench.copy_sweep \
-        --min 4K --max 1G --jsonl gpurun_out/copy_sweep.jsonl --table gpurun_out/variant_table.json
+        --min-bytes 4K --max-bytes 1G --jsonl gpurun_out/copy_sweep.jsonl --table gpurun_out/variant_table.json
 """
 from __future__ import annotations
 
@@ -60,8 +60,8 @@ def time_engine(copies, mode: str, dev: int, iters: int) -> float:
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--min", type=parse_nbytes, default=parse_nbytes("4K"))
-    ap.add_argument("--max", type=parse_nbytes, default=parse_nbytes("1G"))
+    ap.add_argument("--min-bytes", dest="min", type=parse_nbytes, default=parse_nbytes("4K"))
+    ap.add_argument("--max-bytes", dest="max", type=parse_nbytes, default=parse_nbytes("1G"))
     ap.add_argument("--patterns", default="one-to-one,all-to-all,round-robin")
     ap.add_argument("--num-sms", type=int, default=0, help="CTAs for SM kernels (0 = sized per message)")
     ap.add_argument("--rr-bytes", type=parse_nbytes, default=8192)

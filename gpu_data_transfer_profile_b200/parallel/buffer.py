@@ -162,8 +162,11 @@ class Buffer:
         with torch.cuda.device(self.device):
             self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
             self.counters = torch.zeros(8, dtype=torch.int32, device=self.device)
-            self.comm_stream = (torch.cuda.current_stream() if self.world.local
-                                else torch.cuda.Stream(device=self.device))
+            self._side_stream = (torch.cuda.current_stream() if self.world.local
+                                 else torch.cuda.Stream(device=self.device))
+            self.comm_stream = torch.cuda.current_stream()
+        self._async_outstanding = False
+        self._ws = {}
         self.host_word = self.C.host_mapped_alloc(4 * 4096)
         self._epoch = dict(notify=0, dispatch=0, combine=0, barrier=0, ll_dispatch=0, ll_combine=0)
         self._carve: Optional[_Carve] = None
@@ -217,18 +220,25 @@ class Buffer:
         return [self.rank, R, E, E // R, K, T, mode, J, B, H, cap, slot_cap, epoch, self._timeout_ns()]
 
     def _enter(self, previous_event, allocate_on_comm_stream, async_finish):
+        """Pick the stream for this op. Synchronous calls run on the caller's stream (no stream
+        switch, no extra event traffic); `async_finish=True` or a `previous_event` uses the
+        buffer's own communication stream."""
         if allocate_on_comm_stream and not async_finish:
             raise ValueError("allocate_on_comm_stream=True requires async_finish=True")
         compute = torch.cuda.current_stream(self.device)
-        if self.world.local:
-            self.comm_stream = compute       # virtual ranks share whatever stream is current
-        if self.comm_stream != compute:
-            if previous_event is not None and getattr(previous_event, "event", None) is not None:
-                ev = previous_event.event.event
-                if ev is not None:
-                    self.comm_stream.wait_event(ev)
-            else:
-                self.comm_stream.wait_stream(compute)
+        use_side = (async_finish or previous_event is not None) and not self.world.local
+        if not use_side:
+            if self._async_outstanding:
+                compute.wait_stream(self._side_stream)     # earlier async work on this buffer
+                self._async_outstanding = False
+            self.comm_stream = compute
+            return compute
+        self.comm_stream = self._side_stream
+        ev = getattr(getattr(previous_event, "event", None), "event", None)
+        if ev is not None:
+            self.comm_stream.wait_event(ev)
+        else:
+            self.comm_stream.wait_stream(compute)
         return compute
 
     def _exit(self, compute, async_finish, tensors) -> Optional[EventOverlap]:
@@ -238,6 +248,7 @@ class Buffer:
             if isinstance(t, torch.Tensor) and t.is_cuda:
                 t.record_stream(compute)
         if async_finish:
+            self._async_outstanding = True
             return EventOverlap(EventHandle(self.comm_stream), tuple(tensors))
         compute.wait_stream(self.comm_stream)
         return None
@@ -245,6 +256,7 @@ class Buffer:
     def barrier(self) -> None:
         """Device-side barrier over the group on the communication stream."""
         self._epoch["barrier"] += 1
+        self._enter(None, False, False)
         with torch.cuda.stream(self.comm_stream):
             self.C.barrier(self.peers, 0, self.rank, self.group_size, self._epoch["barrier"],
                            self._timeout_ns(), self.status_ptr, not self.world.local)
@@ -252,6 +264,7 @@ class Buffer:
     def probe_timeout(self, timeout_s: float = 0.2) -> int:
         """Wait on a flag that nothing sets, with a short limit; returns the status code that the
         kernel recorded (8) and clears it. Shows that a lost peer ends in an error, not a hang."""
+        self._enter(None, False, False)
         with torch.cuda.stream(self.comm_stream):
             self.C.wait_flags(self.region.local_ptr, 0, self.C.NUM_CHANNELS - 1, 1, 1 << 30,
                               int(timeout_s * 1e9), self.status_ptr, 8)
@@ -274,8 +287,8 @@ class Buffer:
         compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
         with torch.cuda.stream(self.comm_stream):
             T = topk_idx.shape[0]
-            per_rank = torch.empty(R, dtype=torch.int32, device=self.device)
-            per_expert = torch.empty(num_experts, dtype=torch.int32, device=self.device)
+            counts = torch.empty(R + num_experts, dtype=torch.int32, device=self.device)
+            per_rank, per_expert = counts[:R], counts[R:]
             in_rank = torch.empty((T, R), dtype=torch.bool, device=self.device)
             self.C.layout(topk_idx, num_experts, R, per_rank, per_expert, in_rank, self.status_ptr)
         ev = self._exit(compute, async_finish, (per_rank, per_expert, in_rank, topk_idx))
@@ -338,12 +351,20 @@ class Buffer:
         st["epoch_n"] = self._epoch["notify"]
         dev = self.device
         C_chunks = max((T + self.C.CHUNK_TOKENS - 1) // self.C.CHUNK_TOKENS, 1)
-        st["item_rank"] = torch.empty((max(T, 1), J), dtype=torch.int32, device=dev)
-        st["chunk_hist"] = torch.empty((C_chunks, B), dtype=torch.int32, device=dev)
+        key = (max(T, 1), J, C_chunks, B)
+        ws = self._ws.get(key)
+        if ws is None:      # scratch reused by every call of this shape (stream-ordered)
+            ws = (torch.empty((max(T, 1), J), dtype=torch.int32, device=dev),
+                  torch.empty((C_chunks, B), dtype=torch.int32, device=dev))
+            self._ws = {key: ws}
+        st["item_rank"], st["chunk_hist"] = ws
         El = E // R
-        st["meta"] = torch.zeros(2 + El + (El + 1) + (R + 1) + 2 * B, dtype=torch.int32, device=dev)
-        st["send_row"] = torch.empty((max(T, 1), J), dtype=torch.int32, device=dev)
-        st["send_slot"] = torch.empty((max(T, 1), J), dtype=torch.int32, device=dev)
+        n_meta = 2 + El + (El + 1) + (R + 1) + 2 * B
+        n_tj = max(T, 1) * J
+        owned = torch.empty(n_meta + 2 * n_tj, dtype=torch.int32, device=dev)   # handle-owned ints
+        st["meta"] = owned[:n_meta]
+        st["send_row"] = owned[n_meta:n_meta + n_tj].view(max(T, 1), J)
+        st["send_slot"] = owned[n_meta + n_tj:].view(max(T, 1), J)
         regions = carve.region_list(st["epoch_n"] & 1, 0, 0)
         geom = self._geom(E=E, K=K, T=T, mode=mode, H=H, cap=carve.cap, slot_cap=carve.slot_cap,
                           epoch=st["epoch_n"])
@@ -391,7 +412,7 @@ class Buffer:
                 raise EpTimeoutError("b200ep status 1: " + STATUS_TEXT[1])
             if n_recv > carve.cap:
                 raise EpStatusError(f"receive region overflow: {n_recv} rows > capacity {carve.cap}")
-            per_expert_list = [self.C.host_read_i32(self.host_word, 2 + i) for i in range(El)]
+            per_expert_list = self.C.host_read_i32_list(self.host_word, 2, El)
         self.C.wait_flags(self.region.local_ptr, 0, 1, R, st["epoch_d"], self._timeout_ns(),
                           self.status_ptr, 2)
         reg = dict(zip(("flags", "counts", "recv_x", "recv_scales", "recv_topk_idx", "recv_topk_w",
