@@ -35,21 +35,21 @@ def iters_for(nbytes: int) -> int:
 
 
 def time_kernel(fn, iters: int) -> float:
-    fn()
+    """fn(launches) enqueues `launches` back-to-back launches from a native loop."""
+    fn(2)
     torch.cuda.synchronize()
     D.barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    for _ in range(iters):
-        fn()
+    fn(iters)
     b.record()
     b.synchronize()
     D.barrier()
     return a.elapsed_time(b) * 1e-3 / iters
 
 
-def time_engine(copies, mode: str, dev: int, iters: int) -> float:
-    eng = K.CopyEngine(copies, mode, stream_device=dev, use_proxy=True)
+def time_engine(copies, mode: str, dev: int, iters: int, ctas_per_copy: int = 8) -> float:
+    eng = K.CopyEngine(copies, mode, stream_device=dev, use_proxy=True, kernel_ctas_per_copy=ctas_per_copy)
     eng.run(2)
     D.barrier()
     r = eng.run(iters)
@@ -107,14 +107,14 @@ def main() -> int:
                 ce = [(d_t.data_ptr(), w.peer_device(dst_rank), s_t.data_ptr(), w.device.index, n)]
                 variants = {
                     "ce": lambda: time_engine(ce, "separate", w.device.index, it),
-                    "lsu16": lambda: time_kernel(lambda: K.lsu_copy(d_t, s_t, n, ctas=c, threads=512, vec_bytes=16), it),
-                    "lsu32": lambda: time_kernel(lambda: K.lsu_copy(d_t, s_t, n, ctas=c, threads=512, vec_bytes=32), it),
+                    "lsu16": lambda: time_kernel(lambda L: K.lsu_copy(d_t, s_t, n, ctas=c, threads=512, vec_bytes=16, launches=L), it),
+                    "lsu32": lambda: time_kernel(lambda L: K.lsu_copy(d_t, s_t, n, ctas=c, threads=512, vec_bytes=32, launches=L), it),
                 }
                 if n % 16 == 0:
                     tile = min(32768, max(1024, n // max(c, 1) // 16 * 16)) if n >= 16384 else max(16, n)
                     variants["tma_staged"] = lambda: time_kernel(
-                        lambda: K.tma_staged_copy([d_t], s_t, n, tile=tile, stages=K.pick_stages(tile), ctas=c,
-                                                  threads=288, status=status), it)
+                        lambda L: K.tma_staged_copy([d_t], s_t, n, tile=tile, stages=K.pick_stages(tile), ctas=c,
+                                                    threads=288, status=status, launches=L), it)
                 moved = n
             elif pattern == "all-to-all":
                 if world < 2:
@@ -124,14 +124,15 @@ def main() -> int:
                 c = max(1, ctas_for(n * peers) // peers)
                 ce = [(v.data_ptr(), w.peer_device(d), s_t.data_ptr(), w.device.index, n) for v, d in zip(views, order)]
 
-                def lsu_all(vec):
-                    for v in views:
-                        K.lsu_copy(v, s_t, n, ctas=c, threads=512, vec_bytes=vec)
+                def lsu_all(vec, L):
+                    for _ in range(L):
+                        for v in views:
+                            K.lsu_copy(v, s_t, n, ctas=c, threads=512, vec_bytes=vec)
                 variants = {
                     "ce": lambda: time_engine(ce, "separate", w.device.index, it),
                     "ce_graph": lambda: time_engine(ce, "graph", w.device.index, it),
-                    "sm_batched": lambda: time_engine(ce, "kernel", w.device.index, it),
-                    "lsu16": lambda: time_kernel(lambda: lsu_all(16), it),
+                    "sm_batched": lambda: time_engine(ce, "kernel", w.device.index, it, ctas_per_copy=max(c, 1)),
+                    "lsu16": lambda: time_kernel(lambda L: lsu_all(16, L), it),
                 }
                 moved = n * peers
             else:  # round-robin
@@ -142,9 +143,10 @@ def main() -> int:
                 c = ctas_for(n)
                 chunks = P.rr_chunks(n, args.rr_bytes, len(order))
                 variants = {
-                    "lsu_rr": lambda: time_kernel(lambda: K.lsu_rr_copy(views, s_t, n, args.rr_bytes, ctas=c, threads=512), it),
-                    "tma_rr": lambda: time_kernel(lambda: K.tma_staged_copy(
-                        views, s_t, n, rr_bytes=args.rr_bytes, tile=32768, stages=4, ctas=c, threads=288, status=status), it),
+                    "lsu_rr": lambda: time_kernel(lambda L: K.lsu_rr_copy(views, s_t, n, args.rr_bytes, ctas=c, threads=512, launches=L), it),
+                    "tma_rr": lambda: time_kernel(lambda L: K.tma_staged_copy(
+                        views, s_t, n, rr_bytes=args.rr_bytes, tile=32768, stages=4, ctas=c, threads=288, status=status,
+                        launches=L), it),
                 }
                 if len(chunks) <= 1024:
                     ce = [(views[sl].data_ptr() + off, w.peer_device(order[sl]), s_t.data_ptr() + off, w.device.index, ln)

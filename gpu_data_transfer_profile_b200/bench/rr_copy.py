@@ -71,20 +71,22 @@ def main() -> int:
     status = K.StagedStatus(w.device)
     ctas = K.resolve_num_ctas(args.num_sms, w.device)
 
-    def launch(k_iters: int):
+    def launch(k_iters: int, launches: int = 1):
         for i in range(c):
             sv = src[i * n:(i + 1) * n]
             dv = [d[i * n:(i + 1) * n] for d in dst_views]
             if args.method == "lsu":
-                K.lsu_rr_copy(dv, sv, n, args.rr_bytes, ctas=ctas, threads=args.threads_per_cta, iters=k_iters)
+                K.lsu_rr_copy(dv, sv, n, args.rr_bytes, ctas=ctas, threads=args.threads_per_cta, iters=k_iters, launches=launches)
             else:
                 K.tma_staged_copy(dv, sv, n, rr_bytes=args.rr_bytes, tile=args.tma_tile_bytes, piece=piece,
                                   stages=stages, ctas=ctas, threads=staged_threads(args.threads_per_cta),
-                                  iters=k_iters, status=status)
+                                  iters=k_iters, status=status, launches=launches)
 
     def phase(iters: int):
         if args.persistent_kernel:
             launch(iters)
+        elif c == 1:
+            launch(1, iters)          # native back-to-back launches, no interpreter in between
         else:
             for _ in range(iters):
                 launch(1)

@@ -84,21 +84,23 @@ def main() -> int:
     status = K.StagedStatus(w.device)
     ctas = K.resolve_num_ctas(args.num_sms, w.device)
 
-    def launch(iters_in_kernel: int):
+    def launch(iters_in_kernel: int, launches: int = 1):
         for i in range(c):
             sv, dv = s_t[i * n:(i + 1) * n], d_t[i * n:(i + 1) * n]
             if args.method == "lsu":
                 K.lsu_copy(dv, sv, n, ctas=ctas, threads=args.threads_per_cta, iters=iters_in_kernel,
-                           vec_bytes=args.vec_bytes, executor=w.device)
+                           vec_bytes=args.vec_bytes, executor=w.device, launches=launches)
             else:
                 K.tma_staged_copy([dv], sv, n, pull=args.executor == "dst", tile=args.tma_tile_bytes,
                                   piece=piece, stages=stages, ctas=ctas,
                                   threads=staged_threads(args.threads_per_cta), iters=iters_in_kernel,
-                                  status=status)
+                                  status=status, launches=launches)
 
     def phase(iters: int):
         if args.persistent_kernel:
             launch(iters)
+        elif c == 1:
+            launch(1, iters)          # native back-to-back launches, no interpreter in between
         else:
             for _ in range(iters):
                 launch(1)

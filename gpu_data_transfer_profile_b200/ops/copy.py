@@ -38,17 +38,20 @@ def resolve_num_ctas(num_sms: int, device=None) -> int:
 
 
 def lsu_copy(dst: torch.Tensor, src: torch.Tensor, nbytes: int, *, ctas: int = 0, threads: int = 256,
-             iters: int = 1, vec_bytes: int = 16, executor: Optional[torch.device] = None) -> None:
+             iters: int = 1, vec_bytes: int = 16, executor: Optional[torch.device] = None,
+             launches: int = 1) -> None:
+    """`iters` repeats the copy inside ONE launch (persistent mode); `launches` repeats the launch
+    from a native loop."""
     _check_u8(dst, nbytes, "dst")
     _check_u8(src, nbytes, "src")
     ex = executor or src.device
     with torch.cuda.device(ex):
         _ext.load().lsu_copy(dst.data_ptr(), src.data_ptr(), nbytes, resolve_num_ctas(ctas, ex),
-                             threads, iters, vec_bytes)
+                             threads, iters, vec_bytes, launches)
 
 
 def lsu_rr_copy(dsts: Sequence[torch.Tensor], src: torch.Tensor, nbytes: int, rr_bytes: int, *,
-                ctas: int = 0, threads: int = 256, iters: int = 1) -> None:
+                ctas: int = 0, threads: int = 256, iters: int = 1, launches: int = 1) -> None:
     _check_u8(src, nbytes, "src")
     for i, d in enumerate(dsts):
         _check_u8(d, nbytes, f"dst[{i}]")
@@ -56,7 +59,7 @@ def lsu_rr_copy(dsts: Sequence[torch.Tensor], src: torch.Tensor, nbytes: int, rr
         raise ValueError("round-robin chunk size must be positive")
     with torch.cuda.device(src.device):
         _ext.load().lsu_rr_copy([d.data_ptr() for d in dsts], src.data_ptr(), nbytes, rr_bytes,
-                                resolve_num_ctas(ctas, src.device), threads, iters)
+                                resolve_num_ctas(ctas, src.device), threads, iters, launches)
 
 
 def check_staged_constraints(nbytes: int, tile: int, piece: int, stages: int, rr_bytes: int = 0,
@@ -99,7 +102,7 @@ class StagedStatus:
 def tma_staged_copy(dsts: Sequence[torch.Tensor], src: torch.Tensor, nbytes: int, *, pull: bool = False,
                     rr_bytes: int = 0, tile: int = 32768, piece: Optional[int] = None,
                     stages: Optional[int] = None, ctas: int = 0, threads: int = 160, iters: int = 1,
-                    status: Optional[StagedStatus] = None) -> None:
+                    status: Optional[StagedStatus] = None, launches: int = 1) -> None:
     """Push (default): `src` local to the executor, `dsts` may be peers. Pull: `src` may be a
     peer, `dsts[0]` is local to the executor."""
     piece = piece or tile
@@ -113,7 +116,7 @@ def tma_staged_copy(dsts: Sequence[torch.Tensor], src: torch.Tensor, nbytes: int
     with torch.cuda.device(ex):
         _ext.load().tma_staged_copy([d.data_ptr() for d in dsts], src.data_ptr(), nbytes, rr_bytes, pull,
                                     tile, piece, stages, resolve_num_ctas(ctas, ex), threads, iters,
-                                    status.t.data_ptr() if status is not None else 0)
+                                    status.t.data_ptr() if status is not None else 0, launches)
 
 
 class CopyEngine:
