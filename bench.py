@@ -128,8 +128,10 @@ def main() -> int:
     # correctness spot check (identity expert => out = x * number of destination ranks)
     out, handle = step()
     n_dst = handle.is_token_in_rank.sum(1, keepdim=True).float()
-    err = (out.float() - x.float() * n_dst).abs().max().item()
-    ok = D.all_ranks_boolean(err <= (0.5 if args.fp8 else 0.13))
+    want = x.float() * n_dst
+    rel = 0.08 if args.fp8 else 0.02          # fp8 e4m3: 3 mantissa bits per destination copy
+    err = ((out.float() - want).abs() - rel * want.abs()).max().item()
+    ok = D.all_ranks_boolean(err <= (0.15 if args.fp8 else 0.13))
 
     # bytes that cross NVLink per rank and step (dispatch + combine, remote destinations only)
     remote = handle.is_token_in_rank.clone()

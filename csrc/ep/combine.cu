@@ -24,7 +24,12 @@ combine_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, const int* __restric
   int n = *n_recv_ptr;
   if (n > g.cap) n = g.cap;
   const int nvec = row_bytes >> 4;
-  for (int i = gw; i < n; i += nw) {
+  // Rows are grouped by source rank, so consecutive rows go to the SAME peer. Each warp therefore
+  // takes one contiguous slice of the row range: at any instant the running warps cover the whole
+  // range, i.e. every peer at once in proportion to its share (no incast on one peer at a time).
+  const int per_warp = (n + nw - 1) / nw;
+  const int i_end = min(n, (gw + 1) * per_warp);
+  for (int i = gw * per_warp; i < i_end; ++i) {
     const int2 meta = recv_meta[i];
     const int slot = meta.x, s = meta.y;
     if (s < 0 || s >= g.R || slot < 0 || slot >= g.slot_cap) {

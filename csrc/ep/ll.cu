@@ -190,7 +190,13 @@ ll_combine_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
   int total = count[el];
   total = total < 0 ? 0 : (total > (int)cap ? (int)cap : total);
   const int row_bytes = P.H * 2;
-  for (int j = blockIdx.y * nwarps + warp; j < total; j += gridDim.y * nwarps) {
+  // rows of one expert are packed by source rank: give every warp a contiguous slice so that the
+  // warps running at one time address all source ranks, not one after the other
+  const int nslices = gridDim.y * nwarps;
+  const int per = (total + nslices - 1) / nslices;
+  const int j0 = (blockIdx.y * nwarps + warp) * per;
+  const int j1 = min(total, j0 + per);
+  for (int j = j0; j < j1; ++j) {
     const int info = src_info[(size_t)el * cap + j];
     const int s = (info >> 24) & 0xff, t = (info & 0xffffff) >> 5, k = info & 31;
     if (s >= P.R || t >= P.M || k >= P.K) {

@@ -31,6 +31,7 @@ class IterationResult:
     total_ms: float
     output: torch.Tensor
     tokens_per_expert: torch.Tensor
+    fwd_bwd_ms: float = 0.0
 
 
 def run_one_iteration(ctx, manager, experts, args, x, fused: bool) -> IterationResult:
@@ -48,10 +49,14 @@ def run_one_iteration(ctx, manager, experts, args, x, fused: bool) -> IterationR
         e2.record()
         out = manager.combine(y)
     e3.record()
+    e4 = torch.cuda.Event(enable_timing=True)
     if args.backward:
         out.float().mean().backward()
+    e4.record()
     torch.cuda.synchronize()
-    return IterationResult(e0.elapsed_time(e1), e1.elapsed_time(e2), e2.elapsed_time(e3), e0.elapsed_time(e3), out, tpe)
+    r = IterationResult(e0.elapsed_time(e1), e1.elapsed_time(e2), e2.elapsed_time(e3), e0.elapsed_time(e3), out, tpe)
+    r.fwd_bwd_ms = e0.elapsed_time(e4)
+    return r
 
 
 def main() -> int:
@@ -102,11 +107,11 @@ def main() -> int:
     for _ in range(args.warmup_iters):
         one()
     D.barrier(group)
-    acc = [0.0, 0.0, 0.0, 0.0]
+    acc = [0.0, 0.0, 0.0, 0.0, 0.0]
     last = None
     for _ in range(args.benchmark_iters):
         last = one()
-        for i, v in enumerate((last.dispatch_ms, last.expert_ms, last.combine_ms, last.total_ms)):
+        for i, v in enumerate((last.dispatch_ms, last.expert_ms, last.combine_ms, last.total_ms, last.fwd_bwd_ms)):
             acc[i] += v / args.benchmark_iters
     D.barrier(group)
     ok = last.output.shape == (T, H) and bool(torch.isfinite(last.output.float()).all())
@@ -115,14 +120,15 @@ def main() -> int:
     tot_max = D.all_reduce_scalar(acc[3], "max", group)
     if args.print_timing:
         D.ordered_print(f"[rank {rank}] backend={backend} mode={args.dispatcher_mode} fused_combine={fused} "
-                        f"dispatch={acc[0]:.4f} ms expert={acc[1]:.4f} ms combine={acc[2]:.4f} ms total={acc[3]:.4f} ms "
+                        f"dispatch={acc[0]:.4f} ms expert={acc[1]:.4f} ms combine={acc[2]:.4f} ms total={acc[3]:.4f} ms fwd+bwd={acc[4]:.4f} ms "
                         f"tokens_per_expert={last.tokens_per_expert.tolist()[:8]} check={'OK' if ok else 'FAIL'}")
     all_ok = D.all_ranks_boolean(ok)
     flops = 2.0 * int(last.tokens_per_expert.sum()) * H * F * (3 if args.activation == "swiglu" else 2)
     C.emit(rank, dict(bench="moe", ep=args.ep, tokens=T, hidden=H, ffn=F, experts=E, topk=K, backend=backend,
                       mode=args.dispatcher_mode, fused_combine=fused, backward=args.backward,
                       dispatch_ms=acc[0], expert_ms=acc[1], combine_ms=acc[2], total_ms_rank0=acc[3],
-                      total_ms_max_over_ranks=tot_max, expert_tflops_rank0=flops / (acc[1] * 1e-3) / 1e12 if acc[1] else 0,
+                      total_ms_max_over_ranks=tot_max,
+                      fwd_bwd_ms_max_over_ranks=D.all_reduce_scalar(acc[4], "max", group) if args.backward else None, expert_tflops_rank0=flops / (acc[1] * 1e-3) / 1e12 if acc[1] else 0,
                       check=bool(all_ok)), args.jsonl)
     A.release_buffers()
     D.shutdown()
