@@ -74,7 +74,7 @@ def main() -> int:
         print(f"note: --gpus {args.gpus} but WORLD_SIZE {world}; using WORLD_SIZE", file=sys.stderr)
     dev = torch.device("cuda", torch.cuda.current_device())
     T, H, E, K = args.tokens, args.hidden, args.experts, args.topk
-    Buffer.set_num_sms(args.num_sms if args.num_sms > 0 else 64)
+    Buffer.set_num_sms(args.num_sms if args.num_sms > 0 else 132)
 
     cfg = Buffer.get_dispatch_config(world, T, K, E)
     nbytes = cfg.get_nvl_buffer_size_hint(H * 2, world)

@@ -130,7 +130,9 @@ __device__ __forceinline__ bool last_block_arrive(unsigned int* counter, unsigne
     fence_acq_rel_sys();
     unsigned int prev = atomicAdd(counter, 1u);
     is_last = (prev == nblocks - 1);
-    if (is_last) { *counter = 0; fence_acq_rel_sys(); }
+    // The last block only needs to ACQUIRE what the others published on this GPU (they made
+    // their own peer stores system-visible before arriving); its later flag stores are releases.
+    if (is_last) { *counter = 0; asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
   }
   __syncthreads();
   return is_last;

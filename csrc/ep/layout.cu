@@ -116,16 +116,25 @@ __global__ void notify_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers,
 
   if (!last_block_arrive(block_counter, gridDim.x)) return;
 
-  // ---- last block: exclusive scan over chunks, per bucket ----
+  // ---- last block: exclusive scan over chunks, per bucket (one warp per bucket, 32 chunks per
+  // step, coalesced loads issued together; a serial loop here costs one L2 round trip per chunk) ----
   const int C = gridDim.x;
-  for (int b = threadIdx.x; b < B; b += blockDim.x) {
-    int acc = 0;
-    for (int cc = 0; cc < C; ++cc) {
-      const int v = __ldcg(&chunk_hist[(size_t)cc * B + b]);
-      chunk_hist[(size_t)cc * B + b] = acc;
-      acc += v;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int b = warp; b < B; b += nwarps) {
+    int carry = 0;
+    for (int c0 = 0; c0 < C; c0 += 32) {
+      const int cc = c0 + lane;
+      const int v = cc < C ? __ldcg(&chunk_hist[(size_t)cc * B + b]) : 0;
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      if (cc < C) chunk_hist[(size_t)cc * B + b] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
     }
-    hist[b] = acc;  // total per bucket
+    if (lane == 0) hist[b] = carry;  // total per bucket
   }
   __syncthreads();
   const int V = R + E;

@@ -68,28 +68,44 @@ ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
     const char* src = x + (size_t)t * P.H * 2;
     if (P.fp8) {
       const int nsteps = (P.H + 511) / 512;
-      for (int it = warp; it < nsteps; it += nwarps) {
-        const int el = it * 512 + lane * 16;
-        const bool act = el < P.H;
-        uint4 a = make_uint4(0, 0, 0, 0), b = a;
-        if (act) {
-          a = ld_global_nc_v4(src + (size_t)el * 2);
-          b = ld_global_nc_v4(src + (size_t)el * 2 + 16);
+      // up to 4 steps per warp with all loads issued before the first conversion
+      for (int it0 = warp; it0 < nsteps; it0 += 4 * nwarps) {
+        uint4 a[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int el = (it0 + u * nwarps) * 512 + lane * 16;
+          a[u] = make_uint4(0, 0, 0, 0);
+          b[u] = a[u];
+          if (it0 + u * nwarps < nsteps && el < P.H) {
+            a[u] = ld_global_nc_v4(src + (size_t)el * 2);
+            b[u] = ld_global_nc_v4(src + (size_t)el * 2 + 16);
+          }
         }
-        float scale;
-        const uint4 o = cast_block_fp8(a, b, &scale);
-        if (act) {
-          for (int j = 0; j < n; ++j) {
-            st_global_v4(s_dst[j] + el, o);
-            if ((lane & 7) == 0) s_scl[j][el >> 7] = scale;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (it0 + u * nwarps >= nsteps) break;       // uniform per warp
+          const int el = (it0 + u * nwarps) * 512 + lane * 16;
+          float scale;
+          const uint4 o = cast_block_fp8(a[u], b[u], &scale);
+          if (el < P.H) {
+            for (int j = 0; j < n; ++j) {
+              st_global_v4(s_dst[j] + el, o);
+              if ((lane & 7) == 0) s_scl[j][el >> 7] = scale;
+            }
           }
         }
       }
     } else {
       const int nvec = (P.H * 2) >> 4;
-      for (int v = threadIdx.x; v < nvec; v += kLLThreads) {
-        const uint4 val = ld_global_nc_v4(src + ((size_t)v << 4));
-        for (int j = 0; j < n; ++j) st_global_v4(s_dst[j] + ((size_t)v << 4), val);
+      for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * kLLThreads) {
+        uint4 val[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v0 + u * kLLThreads < nvec) val[u] = ld_global_nc_v4(src + ((size_t)(v0 + u * kLLThreads) << 4));
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v0 + u * kLLThreads < nvec)
+            for (int j = 0; j < n; ++j) st_global_v4(s_dst[j] + ((size_t)(v0 + u * kLLThreads) << 4), val[u]);
       }
     }
     __syncthreads();
@@ -102,8 +118,7 @@ ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
     int* dst = reinterpret_cast<int*>(peers.base[e / P.El] + P.count[par]) + (e % P.El) * P.R + P.rank;
     st_relaxed_sys(dst, c);
   }
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();   // the flag stores below are system-scope releases, cumulative over the CTA's stores
   if (threadIdx.x < P.R) {
     int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + P.flags) + kChLLDispatch * kMaxRanks + P.rank;
     st_release_sys(flag, epoch);
@@ -162,8 +177,16 @@ ll_dispatch_recv_kernel(LLParams P, char* self_base, char* __restrict__ out_x,
     const size_t out_row = (size_t)el * cap + j;
     const char* src = self_base + P.recv_x[par] + in_row * row_bytes;
     char* dst = out_x + out_row * row_bytes;
-    for (int v = lane; v < (row_bytes >> 4); v += 32)
-      st_global_v4(dst + ((size_t)v << 4), ld_global_v4(src + ((size_t)v << 4)));
+    const int nv = row_bytes >> 4;
+    for (int v0 = lane; v0 < nv; v0 += 32 * 16) {
+      uint4 buf[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        if (v0 + u * 32 < nv) buf[u] = ld_global_v4(src + ((size_t)(v0 + u * 32) << 4));
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        if (v0 + u * 32 < nv) st_global_v4(dst + ((size_t)(v0 + u * 32) << 4), buf[u]);
+    }
     if (P.fp8) {
       const float* ss = reinterpret_cast<const float*>(self_base + P.recv_scales[par]) + in_row * scale_cols;
       for (int c = lane; c < scale_cols; c += 32) out_scales[out_row * scale_cols + c] = ss[c];
@@ -205,14 +228,15 @@ ll_combine_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
     }
     const char* src = x + ((size_t)el * cap + j) * row_bytes;
     char* dst = peers.base[s] + P.comb_x[par] + ((size_t)t * P.K + k) * row_bytes;
-    for (int v0 = lane; v0 < (row_bytes >> 4); v0 += 128) {
-      uint4 buf[4];
+    const int nv = row_bytes >> 4;
+    for (int v0 = lane; v0 < nv; v0 += 32 * 14) {
+      uint4 buf[14];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (v0 + u * 32 < (row_bytes >> 4)) buf[u] = ld_global_nc_v4(src + ((size_t)(v0 + u * 32) << 4));
+      for (int u = 0; u < 14; ++u)
+        if (v0 + u * 32 < nv) buf[u] = ld_global_nc_v4(src + ((size_t)(v0 + u * 32) << 4));
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (v0 + u * 32 < (row_bytes >> 4)) st_global_v4(dst + ((size_t)(v0 + u * 32) << 4), buf[u]);
+      for (int u = 0; u < 14; ++u)
+        if (v0 + u * 32 < nv) st_global_v4(dst + ((size_t)(v0 + u * 32) << 4), buf[u]);
     }
   }
   if (!last_block_arrive(block_counter, gridDim.x * gridDim.y)) return;
@@ -251,13 +275,21 @@ ll_combine_recv_kernel(LLParams P, char* self_base, const long long* __restrict_
     const char* base = self_base + P.comb_x[par] + (size_t)t * P.K * row_bytes;
     for (int v = threadIdx.x; v < nvec; v += kLLThreads) {
       float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int k = 0; k < P.K; ++k) {
-        const float w = s_w[k];
-        if (w == 0.f) continue;
-        const uint4 val = ld_global_v4(base + (size_t)k * row_bytes + ((size_t)v << 4));
-        const uint32_t u[4] = {val.x, val.y, val.z, val.w};
+      for (int k0 = 0; k0 < P.K; k0 += 8) {
+        uint4 val[8];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) { a[2 * q] += w * bf16lo(u[q]); a[2 * q + 1] += w * bf16hi(u[q]); }
+        for (int u = 0; u < 8; ++u)       // loads first (independent), then the fp32 accumulation
+          if (k0 + u < P.K && s_w[k0 + u] != 0.f)
+            val[u] = ld_global_v4(base + (size_t)(k0 + u) * row_bytes + ((size_t)v << 4));
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (k0 + u >= P.K) break;
+          const float w = s_w[k0 + u];
+          if (w == 0.f) continue;
+          const uint32_t uu[4] = {val[u].x, val[u].y, val[u].z, val[u].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) { a[2 * q] += w * bf16lo(uu[q]); a[2 * q + 1] += w * bf16hi(uu[q]); }
+        }
       }
       uint4 o;
       uint32_t* ou = &o.x;

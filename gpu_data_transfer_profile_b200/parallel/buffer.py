@@ -617,7 +617,7 @@ class Buffer:
             raise ValueError("low-latency combine takes a contiguous bf16 [E_local, R*M, hidden] tensor")
         pv = self._ll_params(st, 0, False)
         self.C.ll_combine_send(pv, self.peers, x, src_info, count, st["epochs"][1:2], st["counters"][1:2],
-                               self.status_ptr, 8)
+                               self.status_ptr, 4)
         return dict(st=st, H=H)
 
     def _ll_combine_recv(self, c, topk_idx, topk_weights, out=None):
