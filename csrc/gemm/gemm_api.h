@@ -31,4 +31,11 @@ struct GemmParams {
 int launch_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, GemmParams p,
                         const PeerPtrs& peers, int ctas, cudaStream_t st);
 
+// SwiGLU x prob elementwise pair for the training path (h: bf16 [rows, 2F], gate columns first).
+// n_rows_ptr (device, optional) bounds the rows actually processed; max_rows is the tensor's size.
+int launch_swiglu_fwd(const void* h, const float* p, void* act, const int* n_rows_ptr, int max_rows, int F,
+                      cudaStream_t st);
+int launch_swiglu_bwd(const void* h, const float* p, const void* dact, void* dh, float* dp, const int* n_rows_ptr,
+                      int max_rows, int F, cudaStream_t st);
+
 }  // namespace b200ep

@@ -36,23 +36,51 @@ def _mlp_backward(x, w1, w2, probs, counts, dy, gated, activation):
     return dx, dw1, dw2, dp
 
 
+def _wgrad(dy, a, counts, out_shape):
+    """dW[e] = dy_e^T @ a_e per local expert (library GEMM; split sizes are host-known here)."""
+    dw = torch.zeros(out_shape, dtype=dy.dtype, device=dy.device)
+    r = 0
+    for e, c in enumerate(counts):
+        if c:
+            torch.mm(dy[r:r + c].t(), a[r:r + c], out=dw[e])
+        r += c
+    return dw
+
+
 class _GroupedMLP(torch.autograd.Function):
+    """Training path. SwiGLU: fc1 (tcgen05, plain epilogue, keeps the pre-activation h) -> fused
+    swiglu x prob kernel -> fc2 (tcgen05). Backward: fused swiglu backward kernel, both dgrads on
+    the tcgen05 grouped GEMM with transposed weights, wgrads with the library GEMM."""
+
     @staticmethod
     def forward(ctx, x, w1, w2, probs, expert_off, counts, activation):
-        if activation == "swiglu":
-            act = G.grouped_gemm_swiglu(x, w1, expert_off, probs)
-        else:
-            h = G.grouped_gemm(x, w1, expert_off)
-            act = (activate(h, activation) * probs[:, None]).to(x.dtype)
-        y = G.grouped_gemm(act, w2, expert_off)
-        ctx.save_for_backward(x, w1, w2, probs)
         ctx.counts, ctx.activation = counts, activation
-        return y
+        ctx.off = expert_off
+        if activation == "swiglu":
+            h = G.grouped_gemm(x, w1, expert_off)
+            act = G.swiglu_fwd(h, probs)
+            y = G.grouped_gemm(act, w2, expert_off)
+            ctx.save_for_backward(x, w1, w2, probs, h, act)
+            return y
+        h = G.grouped_gemm(x, w1, expert_off)
+        act = (activate(h, activation) * probs[:, None]).to(x.dtype)
+        ctx.save_for_backward(x, w1, w2, probs)
+        return G.grouped_gemm(act, w2, expert_off)
 
     @staticmethod
     def backward(ctx, dy):
-        x, w1, w2, probs = ctx.saved_tensors
-        dx, dw1, dw2, dp = _mlp_backward(x, w1, w2, probs, ctx.counts, dy.contiguous(), True, ctx.activation)
+        dy = dy.contiguous()
+        if ctx.activation != "swiglu":
+            x, w1, w2, probs = ctx.saved_tensors
+            dx, dw1, dw2, dp = _mlp_backward(x, w1, w2, probs, ctx.counts, dy, False, ctx.activation)
+            return dx, dw1, dw2, dp, None, None, None
+        x, w1, w2, probs, h, act = ctx.saved_tensors
+        rows = sum(ctx.counts)
+        dact = G.grouped_gemm(dy, w2.transpose(1, 2).contiguous(), ctx.off)          # [rows, F]
+        dh, dp = G.swiglu_bwd(h, probs, dact)
+        dx = G.grouped_gemm(dh, w1.transpose(1, 2).contiguous(), ctx.off)            # [rows, H]
+        dw2 = _wgrad(dy[:rows], act[:rows], ctx.counts, w2.shape)
+        dw1 = _wgrad(dh[:rows], x[:rows], ctx.counts, w1.shape)
         return dx, dw1, dw2, dp, None, None, None
 
 

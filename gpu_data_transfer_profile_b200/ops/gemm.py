@@ -55,3 +55,18 @@ def grouped_gemm_combine(a: torch.Tensor, w: torch.Tensor, expert_off: torch.Ten
     recv_meta[r,0] of rank recv_meta[r,1]'s combine region (peer LSU stores)."""
     _ext.load().grouped_gemm(a, w, expert_off, COMBINE, None, None, recv_meta, list(peers), comb_off, slot_cap,
                              rank, signal_flag_off, epoch, counter, status_ptr, ctas or _ctas(a.device))
+
+
+def swiglu_fwd(h: torch.Tensor, row_prob: Optional[torch.Tensor]) -> torch.Tensor:
+    """act = silu(h[:, :F]) * h[:, F:] * row_prob[:, None]  (bf16 in, bf16 out)."""
+    act = torch.empty((h.shape[0], h.shape[1] // 2), dtype=torch.bfloat16, device=h.device)
+    _ext.load().swiglu_fwd(h, row_prob, act)
+    return act
+
+
+def swiglu_bwd(h: torch.Tensor, row_prob: Optional[torch.Tensor], dact: torch.Tensor):
+    """-> (dh bf16 [rows, 2F], dprob f32 [rows]) for act = swiglu(h) * prob."""
+    dh = torch.empty_like(h)
+    dp = torch.empty(h.shape[0], dtype=torch.float32, device=h.device)
+    _ext.load().swiglu_bwd(h, row_prob, dact.contiguous(), dh, dp)
+    return dh, dp

@@ -51,3 +51,49 @@ def test_grouped_gemm_rejects_bad_shapes():
     w = torch.zeros(1, 64, 36, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):
         G.grouped_gemm(a, w, G.offsets_from_counts([8], "cuda"))
+
+
+def test_swiglu_fwd_bwd_kernels_match_autograd():
+    from gpu_data_transfer_profile_b200.ops import gemm as G
+    torch.manual_seed(2)
+    rows, F = 37, 264
+    h = torch.randn(rows, 2 * F, device="cuda").to(torch.bfloat16)
+    p = torch.rand(rows, device="cuda")
+    dact = torch.randn(rows, F, device="cuda").to(torch.bfloat16)
+    hf = h.float().requires_grad_(True)
+    pf = p.clone().requires_grad_(True)
+    ref = torch.nn.functional.silu(hf[:, :F]) * hf[:, F:] * pf[:, None]
+    rdh, rdp = torch.autograd.grad(ref, [hf, pf], dact.float())
+    act = G.swiglu_fwd(h, p)
+    dh, dp = G.swiglu_bwd(h, p, dact)
+    torch.testing.assert_close(act.float(), ref.detach(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(dh.float(), rdh, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(dp, rdp, atol=0.3, rtol=2e-2)
+
+
+def test_tcgen05_experts_backward_matches_torch_experts():
+    from gpu_data_transfer_profile_b200.models.experts import TorchGroupedExperts
+    from gpu_data_transfer_profile_b200.models.experts_tcgen05 import Tcgen05GroupedExperts
+    torch.manual_seed(3)
+    E, H, F = 3, 256, 384
+    counts = [70, 0, 131]
+    rows = sum(counts)
+    a = Tcgen05GroupedExperts(E, H, F, torch.bfloat16, "swiglu", init_std=0.05)
+    b = TorchGroupedExperts(E, H, F, torch.float32, "swiglu")
+    with torch.no_grad():
+        b.weight1.copy_(a.weight1.float())
+        b.weight2.copy_(a.weight2.float())
+    x = torch.randn(rows, H, device="cuda")
+    p = torch.rand(rows, device="cuda")
+    xa, pa = x.to(torch.bfloat16).requires_grad_(True), p.clone().requires_grad_(True)
+    xb, pb = x.to(torch.bfloat16).float().requires_grad_(True), p.clone().requires_grad_(True)
+    g = torch.randn(rows, H, device="cuda")
+    ya = a(xa, counts, pa)
+    yb = b(xb, counts, pb)
+    ya.backward(g.to(torch.bfloat16))
+    yb.backward(g.to(torch.bfloat16).float())
+    torch.testing.assert_close(ya.float(), yb, atol=5e-2, rtol=5e-2)
+    torch.testing.assert_close(xa.grad.float(), xb.grad, atol=5e-2, rtol=5e-2)
+    torch.testing.assert_close(pa.grad, pb.grad, atol=0.5, rtol=5e-2)
+    torch.testing.assert_close(a.weight1.grad.float(), b.weight1.grad, atol=0.15, rtol=5e-2)
+    torch.testing.assert_close(a.weight2.grad.float(), b.weight2.grad, atol=0.15, rtol=5e-2)
