@@ -21,6 +21,11 @@ int launch_tma_staged_copy(void* const* dsts, int n_dst, const void* src, long l
                            long long rr_bytes, int pull, int tile, int piece, int stages, int ctas,
                            int threads, int iters, int* status, cudaStream_t st);
 
+// Broadcast src[0:n] to offset 0.. of EVERY GPU bound to the multicast address mc_dst
+// (16-byte multiples, `multimem.st`). The caller orders completion (stream sync + barrier).
+int launch_multimem_bcast(void* mc_dst, const void* src, long long nbytes, int ctas, int threads, int iters,
+                          cudaStream_t st);
+
 // One launch that performs a table of independent copies (the SM stand-in for a batched
 // memcpy submission). desc is a DEVICE array of n entries.
 struct CopyDesc { void* dst; const void* src; long long nbytes; };

@@ -65,6 +65,7 @@ def main() -> int:
     ap.add_argument("--patterns", default="one-to-one,all-to-all,round-robin")
     ap.add_argument("--num-sms", type=int, default=0, help="CTAs for SM kernels (0 = sized per message)")
     ap.add_argument("--rr-bytes", type=parse_nbytes, default=8192)
+    ap.add_argument("--no-multimem", action="store_true", help="skip the NVSwitch multicast variant")
     ap.add_argument("--jsonl", default=None)
     ap.add_argument("--table", default=None)
     args = ap.parse_args()
@@ -76,6 +77,13 @@ def main() -> int:
     src.copy_(CC.position_pattern(src.numel(), rank, w.device))
     status = K.StagedStatus(w.device)
     sms = K.sm_count(w.device)
+    mc = None
+    if world > 1 and "all-to-all" in args.patterns and not args.no_multimem:
+        mc = K.MulticastBuffer(max(sizes) * world)
+        if not D.all_ranks_boolean(mc.available):
+            if rank == 0:
+                print(f"[sweep] multimem variant skipped: {mc.why or 'no multicast mapping on a peer'}", flush=True)
+            mc = None
     records, table = [], {}
 
     def ctas_for(n: int) -> int:
@@ -134,6 +142,10 @@ def main() -> int:
                     "sm_batched": lambda: time_engine(ce, "kernel", w.device.index, it, ctas_per_copy=max(c, 1)),
                     "lsu16": lambda: time_kernel(lambda L: lsu_all(16, L), it),
                 }
+                if mc is not None and n % 16 == 0:
+                    cm = ctas_for(n)
+                    variants["multimem"] = lambda: time_kernel(
+                        lambda L: mc.broadcast(s_t, n, offset=rank * n, ctas=cm, threads=512, launches=L), it)
                 moved = n * peers
             else:  # round-robin
                 if world < 2 or n % 16 or n < args.rr_bytes:

@@ -151,3 +151,42 @@ def enable_peer_access(dev: int, peer: int) -> None:
     rc = C.enable_peer_access(dev, peer)
     if rc:
         raise RuntimeError(f"cudaDeviceEnablePeerAccess({dev}->{peer}) failed with {rc}")
+
+
+class MulticastBuffer:
+    """A symmetric buffer with an NVSwitch multicast mapping (NVLS), obtained from PyTorch's
+    symmetric-memory allocator. `available` is False when the platform offers no multicast
+    (single GPU, no NVSwitch, or the allocator cannot exchange handles): callers then fall back
+    to unicast variants. Collective: every rank of `group` must construct it."""
+
+    def __init__(self, nbytes: int, group=None, device=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.available, self.why = False, ""
+        self.nbytes = int(nbytes)
+        try:
+            grp = group if group is not None else dist.group.WORLD
+            self.tensor = symm.empty(self.nbytes, dtype=torch.uint8, device=device or torch.device("cuda", torch.cuda.current_device()))
+            self.handle = symm.rendezvous(self.tensor, grp)
+            self.multicast_ptr = int(self.handle.multicast_ptr)
+            self.available = self.multicast_ptr != 0
+            if not self.available:
+                self.why = "allocator reports no multicast support"
+        except Exception as e:  # pragma: no cover - depends on the platform
+            self.tensor, self.handle, self.multicast_ptr = None, None, 0
+            self.why = f"{type(e).__name__}: {e}"
+
+    def broadcast(self, src: torch.Tensor, nbytes: int, offset: int = 0, *, ctas: int = 0, threads: int = 512,
+                  iters: int = 1, launches: int = 1) -> None:
+        """Store src[0:nbytes] to [offset, offset+nbytes) of this buffer on EVERY rank."""
+        if not self.available:
+            raise RuntimeError(f"multicast unavailable: {self.why}")
+        _check_u8(src, nbytes, "src")
+        if offset % 16 or nbytes % 16 or offset + nbytes > self.nbytes:
+            raise ValueError("offset and size must be multiples of 16 inside the buffer")
+        _ext.load().multimem_bcast(self.multicast_ptr + offset, src.data_ptr(), nbytes,
+                                   resolve_num_ctas(ctas, src.device), threads, iters, launches)
+
+    def barrier(self):
+        if self.handle is not None:
+            self.handle.barrier()

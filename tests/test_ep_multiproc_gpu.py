@@ -93,3 +93,15 @@ def test_copy_clis_two_gpus(mod, extra):
     r = _torchrun(2, ["-m", f"gpu_data_transfer_profile_b200.bench.{mod}", "--iters", "5", "--warmup", "2", "--check"] + extra)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "check=OK" in r.stdout and "check=FAIL" not in r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
+def test_multimem_fanout_two_gpus():
+    """Switch-multicast broadcast: exit code 3 = the platform offers no multicast mapping (not a failure)."""
+    r = _torchrun(2, ["-m", "gpu_data_transfer_profile_b200.bench.a2a_copy", "--copy-mode", "multimem", "--nbytes", "1M",
+                      "--iters", "5", "--warmup", "2", "--check"])
+    assert r.returncode in (0, 3), r.stdout[-3000:] + r.stderr[-3000:]
+    if r.returncode == 0:
+        assert "check=OK" in r.stdout and "check=FAIL" not in r.stdout
+    else:
+        assert "multimem unavailable" in r.stdout
