@@ -67,6 +67,8 @@ def main() -> int:
     ap.add_argument("--rr-bytes", type=parse_nbytes, default=8192)
     ap.add_argument("--no-multimem", action="store_true", help="skip the NVSwitch multicast variant")
     ap.add_argument("--jsonl", default=None)
+    ap.add_argument("--resume", action="store_true",
+                    help="skip (pattern, size) pairs that the --jsonl file already holds (continue an interrupted sweep)")
     ap.add_argument("--table", default=None)
     args = ap.parse_args()
     rank, world, _ = D.env_rank_info()
@@ -104,8 +106,23 @@ def main() -> int:
                 with open(args.jsonl, "a") as f:
                     f.write(json.dumps(rec) + "\n")
 
+    done = set()
+    if args.resume and args.jsonl:
+        import os
+        if os.path.exists(args.jsonl):
+            for line in open(args.jsonl):
+                if line.strip():
+                    r = json.loads(line)
+                    if r.get("world") == world:
+                        done.add((r["pattern"], r["nbytes"]))
+                        records.append(r)
     for pattern in args.patterns.split(","):
         for n in sizes:
+            if (pattern, n) in done:
+                prev = [r for r in records if r["pattern"] == pattern and r["nbytes"] == n]
+                b = min(prev, key=lambda r: r["seconds_slowest"])
+                table.setdefault(pattern, []).append({"nbytes": n, "variant": b["variant"], "seconds": b["seconds_slowest"]})
+                continue
             it = iters_for(n)
             s_t = src[:n]
             if pattern == "one-to-one":

@@ -118,6 +118,23 @@ class _Carve:
 _ELEM_DTYPE = {torch.bfloat16: "bfloat16", torch.float16: "float16", torch.float32: "float32"}
 
 
+def _nvtx(name):
+    """NVTX range around a public op so that profiler timelines show dispatch / combine blocks
+    (the reference relies on a dedicated stream for readability, `Copy_Engine/nvlink_copy_engine_test.py:528-530`)."""
+    def deco(fn):
+        import functools
+
+        @functools.wraps(fn)
+        def wrapped(*a, **k):
+            torch.cuda.nvtx.range_push(name)
+            try:
+                return fn(*a, **k)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        return wrapped
+    return deco
+
+
 class Buffer:
     num_sms: int = 24
 
@@ -273,6 +290,7 @@ class Buffer:
         return code
 
     # ---- layout ----------------------------------------------------------------------
+    @_nvtx("b200ep.layout")
     def get_dispatch_layout(self, topk_idx: torch.Tensor, num_experts: int,
                             previous_event=None, async_finish: bool = False,
                             allocate_on_comm_stream: bool = False):
@@ -438,6 +456,7 @@ class Buffer:
                                 per_expert_list, st["fp8"], recv_prob)
         return recv_x, recv_topk_idx, recv_topk_w, per_expert_list, handle
 
+    @_nvtx("b200ep.dispatch")
     def dispatch(self, x, handle: Optional[DispatchHandle] = None, num_tokens_per_rank=None,
                  num_tokens_per_rdma_rank=None, is_token_in_rank=None, num_tokens_per_expert=None,
                  topk_idx=None, topk_weights=None, expert_alignment: int = 1, num_worst_tokens: int = 0,
@@ -497,6 +516,7 @@ class Buffer:
                               weights, out, out_w, st["ep"], self.status_ptr, self._blocks() * 2)
         return out, out_w
 
+    @_nvtx("b200ep.combine")
     def combine(self, x, handle: DispatchHandle, topk_weights=None, bias=None,
                 config: Optional[Config] = None, previous_event=None, async_finish: bool = False,
                 allocate_on_comm_stream: bool = False, *, item_weights=None):
@@ -586,6 +606,7 @@ class Buffer:
         handle = (out_src, out_range, M, H, d["E"], out_count, d["K"])
         return ((out_x, out_s) if d["fp8"] else out_x), out_count, handle
 
+    @_nvtx("b200ep.ll_dispatch")
     def low_latency_dispatch(self, x, topk_idx, num_max_dispatch_tokens_per_rank: int, num_experts: int,
                              use_fp8: bool = True, async_finish: bool = False,
                              return_recv_hook: bool = False):
@@ -631,6 +652,7 @@ class Buffer:
                                self.status_ptr, max(Buffer.num_sms * 4, 1))
         return out
 
+    @_nvtx("b200ep.ll_combine")
     def low_latency_combine(self, x, topk_idx, topk_weights, handle, async_finish: bool = False,
                             return_recv_hook: bool = False, out: Optional[torch.Tensor] = None):
         """-> (combined_x [T,H] bf16 = sum_k topk_weights[t,k] * expert output of (t,k), event, hook)."""

@@ -116,3 +116,29 @@ def test_variant_selector_uses_nearest_measured_size():
     with pytest.raises(KeyError):
         V.select("ring-of-fire", 1, table)
     assert V.select("round-robin", 1 << 20) in ("lsu_rr", "tma_rr", "ce_graph")
+
+
+def test_deep_ep_compat_module_exposes_the_api_the_reference_imports():
+    import importlib
+    import os
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "deep_ep_compat"))
+    try:
+        deep_ep = importlib.import_module("deep_ep")
+        utils = importlib.import_module("deep_ep.utils")
+        import torch
+        assert deep_ep.topk_idx_t == torch.int64
+        for name in ("set_num_sms", "get_dispatch_config", "get_combine_config", "get_dispatch_layout", "dispatch",
+                     "combine", "low_latency_dispatch", "low_latency_combine"):
+            assert hasattr(deep_ep.Buffer, name)
+        cfg = deep_ep.Buffer.get_dispatch_config(8)
+        assert cfg.get_nvl_buffer_size_hint(7168 * 2, 8) > 0 and cfg.get_rdma_buffer_size_hint(7168 * 2, 8) == 0
+        assert utils.EventOverlap(utils.EventHandle()) is not None
+        deep_ep.Buffer.set_num_sms(24)
+        with pytest.raises(ValueError):
+            deep_ep.Buffer.set_num_sms(0)
+    finally:
+        sys.path.pop(0)
+        sys.modules.pop("deep_ep", None)
+        sys.modules.pop("deep_ep.utils", None)
