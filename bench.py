@@ -54,6 +54,8 @@ def main() -> int:
     ap.add_argument("--num-sms", type=int, default=0, help="CTA budget knob (0 = tuned default)")
     ap.add_argument("--fp8", action="store_true", help="secondary: fp8 e4m3 1x128 dispatch")
     ap.add_argument("--zipf", type=float, default=0.0)
+    ap.add_argument("--host-count", action="store_true",
+                    help="size the outputs from a host read of the receive count instead of num_worst_tokens")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -92,13 +94,15 @@ def main() -> int:
     result_h = torch.zeros(1, dtype=torch.float32).pin_memory()
 
     expert_out = {}
+    # receive bound for the sync-free path: every token of every rank (no host read of the count)
+    worst = 0 if args.host_count else world * T
 
     def step(xd=x, idxd=idx, wd=w):
         per_rank, _, per_expert, in_rank, _ = buf.get_dispatch_layout(idxd, E)
         recv_x, _, _, _, handle, _ = buf.dispatch(
             xd, topk_idx=idxd, topk_weights=wd, num_tokens_per_rank=per_rank,
             is_token_in_rank=in_rank, num_tokens_per_expert=per_expert, use_fp8=args.fp8,
-            zero_copy=True)
+            zero_copy=True, num_worst_tokens=worst)
         if args.fp8:
             # experts consume fp8 + scales and emit bf16; the stand-in expert output is the bf16
             # dequantisation of the received rows, computed once (routing and tokens are fixed)
@@ -153,7 +157,8 @@ def main() -> int:
             "config": {"model": MODEL, "global_batch": int(total_tokens), "seq_len": T,
                        "parallelism": f"ep{world}", "hidden": H, "experts": E, "topk": K,
                        "zipf_s": args.zipf, "l2": "flushed between steps (252 MiB write)",
-                       "receive": "zero-copy views of the symmetric receive region",
+                       "receive": "zero-copy views of the symmetric receive region, "
+                                  + ("sized by a host read of the count" if args.host_count else "num_worst_tokens = world x tokens (no host sync)"),
                        "num_sms_knob": Buffer.num_sms},
             "tokens_per_s": round(total_tokens / (ms * 1e-3), 1),
             "nvlink_gbs_per_rank": round(nv_bytes_max / (ms * 1e-3) / 1e9, 2),

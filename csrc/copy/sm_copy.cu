@@ -25,6 +25,9 @@ namespace b200ep {
 template <int VEC>  // 16 or 32 bytes per access; 1 = byte fallback
 __global__ void lsu_copy_kernel(char* __restrict__ dst, const char* __restrict__ src,
                                 long long nbytes, int iters) {
+  // When launched with programmatic stream serialisation the next launch in the stream may
+  // start as soon as every CTA has passed this point (independent copies need no further wait).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nth = (long long)gridDim.x * blockDim.x;
   for (int it = 0; it < iters; ++it) {
@@ -60,18 +63,42 @@ __global__ void lsu_copy_kernel(char* __restrict__ dst, const char* __restrict__
   }
 }
 
+template <int VEC>
+static void lsu_launch(char* d, const char* s, long long nbytes, int ctas, int threads, int iters, bool overlap,
+                       cudaStream_t st) {
+  if (!overlap) {
+    lsu_copy_kernel<VEC><<<ctas, threads, 0, st>>>(d, s, nbytes, iters);
+    return;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctas);
+  cfg.blockDim = dim3(threads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, lsu_copy_kernel<VEC>, d, s, nbytes, iters);
+}
+
+// vec_bytes: 16 or 32; add 256 to let consecutive launches in the stream overlap (programmatic
+// dependent launch): meant for back-to-back INDEPENDENT copies, where the launch latency and the
+// drain of the previous kernel otherwise dominate small messages.
 int launch_lsu_copy(void* dst, const void* src, long long nbytes, int ctas, int threads,
                     int iters, int vec_bytes, cudaStream_t st) {
   if (nbytes <= 0 || ctas <= 0 || threads <= 0 || threads > 1024 || iters <= 0) return 1;
+  const bool overlap = (vec_bytes & 256) != 0;
+  vec_bytes &= 255;
   const uintptr_t a = reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src);
   char* d = static_cast<char*>(dst);
   const char* s = static_cast<const char*>(src);
   if (vec_bytes == 32 && (a % 32) == 0)
-    lsu_copy_kernel<32><<<ctas, threads, 0, st>>>(d, s, nbytes, iters);
+    lsu_launch<32>(d, s, nbytes, ctas, threads, iters, overlap, st);
   else if (vec_bytes >= 16 && (a % 16) == 0)
-    lsu_copy_kernel<16><<<ctas, threads, 0, st>>>(d, s, nbytes, iters);
+    lsu_launch<16>(d, s, nbytes, ctas, threads, iters, overlap, st);
   else
-    lsu_copy_kernel<1><<<ctas, threads, 0, st>>>(d, s, nbytes, iters);
+    lsu_launch<1>(d, s, nbytes, ctas, threads, iters, overlap, st);
   return 0;
 }
 

@@ -134,6 +134,8 @@ def main() -> int:
                     "ce": lambda: time_engine(ce, "separate", w.device.index, it),
                     "lsu16": lambda: time_kernel(lambda L: K.lsu_copy(d_t, s_t, n, ctas=c, threads=512, vec_bytes=16, launches=L), it),
                     "lsu32": lambda: time_kernel(lambda L: K.lsu_copy(d_t, s_t, n, ctas=c, threads=512, vec_bytes=32, launches=L), it),
+                    "lsu16_overlap": lambda: time_kernel(lambda L: K.lsu_copy(
+                        d_t, s_t, n, ctas=c, threads=512, vec_bytes=16, launches=L, overlap_launches=True), it),
                 }
                 if n % 16 == 0:
                     tile = min(32768, max(1024, n // max(c, 1) // 16 * 16)) if n >= 16384 else max(16, n)

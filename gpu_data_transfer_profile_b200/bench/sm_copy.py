@@ -36,6 +36,8 @@ def add_sm_flags(ap: argparse.ArgumentParser, executor_default: str) -> None:
     ap.add_argument("--tma-inter-tile-bytes", type=parse_nbytes, default=None)
     ap.add_argument("--tma-stages", type=int, default=0, help="pipeline depth (0 = as many as fit, max 4)")
     ap.add_argument("--persistent-kernel", action="store_true")
+    ap.add_argument("--overlap-launches", action="store_true",
+                    help="LSU method: let consecutive launches overlap (programmatic dependent launch)")
     ap.add_argument("--mode", choices=list(P.PAIR_MODES), default="ring")
 
 
@@ -89,7 +91,8 @@ def main() -> int:
             sv, dv = s_t[i * n:(i + 1) * n], d_t[i * n:(i + 1) * n]
             if args.method == "lsu":
                 K.lsu_copy(dv, sv, n, ctas=ctas, threads=args.threads_per_cta, iters=iters_in_kernel,
-                           vec_bytes=args.vec_bytes, executor=w.device, launches=launches)
+                           vec_bytes=args.vec_bytes, executor=w.device, launches=launches,
+                           overlap_launches=args.overlap_launches)
             else:
                 K.tma_staged_copy([dv], sv, n, pull=args.executor == "dst", tile=args.tma_tile_bytes,
                                   piece=piece, stages=stages, ctas=ctas,

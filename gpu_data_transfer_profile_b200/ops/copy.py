@@ -39,15 +39,16 @@ def resolve_num_ctas(num_sms: int, device=None) -> int:
 
 def lsu_copy(dst: torch.Tensor, src: torch.Tensor, nbytes: int, *, ctas: int = 0, threads: int = 256,
              iters: int = 1, vec_bytes: int = 16, executor: Optional[torch.device] = None,
-             launches: int = 1) -> None:
+             launches: int = 1, overlap_launches: bool = False) -> None:
     """`iters` repeats the copy inside ONE launch (persistent mode); `launches` repeats the launch
-    from a native loop."""
+    from a native loop; `overlap_launches` lets consecutive launches overlap (programmatic
+    dependent launch) - only for copies that do not depend on each other."""
     _check_u8(dst, nbytes, "dst")
     _check_u8(src, nbytes, "src")
     ex = executor or src.device
     with torch.cuda.device(ex):
         _ext.load().lsu_copy(dst.data_ptr(), src.data_ptr(), nbytes, resolve_num_ctas(ctas, ex),
-                             threads, iters, vec_bytes, launches)
+                             threads, iters, vec_bytes | (256 if overlap_launches else 0), launches)
 
 
 def lsu_rr_copy(dsts: Sequence[torch.Tensor], src: torch.Tensor, nbytes: int, rr_bytes: int, *,

@@ -414,13 +414,19 @@ class Buffer:
                              st.get("chunk_hist"), st["send_row"], st["send_slot"],
                              self.counters[1:2], self.status_ptr, self._blocks())
 
-    def _dispatch_p3(self, st, zero_copy: bool):
+    def _dispatch_p3(self, st, zero_copy: bool, num_worst_tokens: int = 0):
         R, E, K, H = self.group_size, st["E"], st["K"], st["H"]
         El = E // R
         carve = st["carve"]
         if st["cached"]:
             h = st["handle"]
             n_recv, per_expert_list = h.n_recv, h.num_recv_tokens_per_expert_list
+        elif num_worst_tokens > 0:
+            # No host synchronisation: outputs are sized for the caller's bound, the true count
+            # stays on the device (handle.n_recv_dev) and rows beyond it are unspecified.
+            if num_worst_tokens > carve.cap:
+                raise ValueError(f"num_worst_tokens={num_worst_tokens} exceeds the buffer capacity {carve.cap}")
+            n_recv, per_expert_list = int(num_worst_tokens), []
         else:
             if not self.C.host_wait_ge(self.host_word, 0, st["epoch_n"], self.timeout_s + 5.0):
                 raise EpTimeoutError("host timed out waiting for the receive count")
@@ -471,13 +477,15 @@ class Buffer:
         `group_by_expert=True`: one row per (token, expert), rows grouped by local expert;
         the per-row router probability is in `handle.recv_prob`.
         `zero_copy=True` returns views into the symmetric region that stay valid until the second
-        next dispatch on this buffer."""
+        next dispatch on this buffer. `num_worst_tokens > 0` removes the host read of the receive
+        count: outputs have exactly that many rows (a bound chosen by the caller, e.g. group_size x
+        tokens per rank), the per-expert list is empty and the true count is `handle.n_recv_dev`."""
         compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
         with torch.cuda.stream(self.comm_stream):
             st = self._dispatch_p1(x, handle, is_token_in_rank, num_tokens_per_expert, topk_idx,
                                    topk_weights, use_fp8, group_by_expert, num_experts)
             self._dispatch_p2(st)
-            out = self._dispatch_p3(st, zero_copy)
+            out = self._dispatch_p3(st, zero_copy, num_worst_tokens)
         flat = []
         for o in out[:3]:
             flat.extend(o if isinstance(o, tuple) else (o,))

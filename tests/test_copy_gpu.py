@@ -118,3 +118,13 @@ def test_copy_clis_single_process(mod, extra):
                        timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "check=OK" in r.stdout and "[aggregate]" in r.stdout
+
+
+def test_lsu_copy_overlapping_launches():
+    from gpu_data_transfer_profile_b200.ops import copy as K
+    n = 1 << 20
+    src = _pattern(n, 9)
+    dst = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    K.lsu_copy(dst, src, n, ctas=16, threads=512, launches=5, overlap_launches=True)
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src)

@@ -145,3 +145,29 @@ def test_lost_peer_is_an_error_not_a_hang():
         g.check_status()
     finally:
         g.destroy()
+
+
+def test_dispatch_without_host_sync_num_worst_tokens():
+    """num_worst_tokens: outputs sized by the caller's bound, true count only on the device."""
+    from gpu_data_transfer_profile_b200.parallel.buffer import Buffer
+    from gpu_data_transfer_profile_b200.parallel.symm import LocalWorld
+    T, H, E, K = 100, 256, 8, 2
+    buf = Buffer(None, 32 << 20, world=LocalWorld.make(1)[0], timeout_s=2.0)
+    try:
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        idx, w = O.make_routing(T, E, K, 3)
+        idx, w = idx.cuda(), w.cuda()
+        pr, _, pe, inr, _ = buf.get_dispatch_layout(idx, E)
+        rx, ri, rw, cnt, h, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_tokens_per_rank=pr, is_token_in_rank=inr,
+                                            num_tokens_per_expert=pe, num_worst_tokens=256, zero_copy=True)
+        assert rx.shape == (256, H) and cnt == [] and h.n_recv == 256
+        assert int(h.n_recv_dev.item()) == T
+        assert torch.equal(rx[:T], x)
+        out, _, _ = buf.combine(rx, h)
+        torch.testing.assert_close(out.float(), x.float())
+        with pytest.raises(ValueError):
+            buf.dispatch(x, topk_idx=idx, topk_weights=w, num_tokens_per_rank=pr, is_token_in_rank=inr,
+                         num_tokens_per_expert=pe, num_worst_tokens=1 << 30)
+        buf.check_status()
+    finally:
+        buf.destroy()
