@@ -27,7 +27,8 @@ void launch_dispatch_send(const EpGeom& g, const EpRegions& rg, const PeerPtrs& 
                           const EpMeta& m, const char* x, int row_bytes_in, bool fp8, bool cached,
                           const long long* topk_idx, const float* topk_w, const int* item_rank,
                           const int* chunk_base, int* send_row, int* send_slot,
-                          unsigned int* block_counter, int* status, int blocks, cudaStream_t st);
+                          unsigned int* block_counter, int* status, int blocks, cudaStream_t st,
+                          const float* scales_in = nullptr);
 
 void launch_combine_send(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers,
                          const int* n_recv_ptr, const int* recv_meta, const char* x, int row_bytes,

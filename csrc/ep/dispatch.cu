@@ -21,7 +21,8 @@ dispatch_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, EpMeta m,
                      const char* __restrict__ x, int row_bytes_in,
                      const long long* __restrict__ topk_idx, const float* __restrict__ topk_w,
                      const int* __restrict__ item_rank, const int* __restrict__ chunk_base,
-                     int* send_row, int* send_slot, unsigned int* block_counter, int* status) {
+                     int* send_row, int* send_slot, unsigned int* block_counter, int* status,
+                     const float* __restrict__ scales_in) {
   __shared__ char* s_dst[kSendWarps][kMaxItemsPerToken];
   __shared__ float* s_scl[kSendWarps][kMaxItemsPerToken];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -101,6 +102,13 @@ dispatch_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, EpMeta m,
           }
         }
       }
+      if (scales_in != nullptr) {
+        // input was quantised by the caller: its per-128-channel scales travel with the row
+        for (int c = lane; c < scale_cols; c += 32) {
+          const float sc = scales_in[(size_t)t * scale_cols + c];
+          for (unsigned mm = vmask; mm; mm &= mm - 1) s_scl[warp][__ffs(mm) - 1][c] = sc;
+        }
+      }
     } else {
       // 16 bf16 per lane per step; 8 lanes share one 128-channel scale block.
       const int nsteps = (g.H + 511) / 512;
@@ -138,13 +146,14 @@ dispatch_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, EpMeta m,
 #define B200EP_LAUNCH_DISPATCH(MODE, FP8, CACHED)                                              \
   dispatch_send_kernel<MODE, FP8, CACHED><<<blocks, kSendWarps * 32, 0, st>>>(                 \
       g, rg, peers, m, x, row_bytes_in, topk_idx, topk_w, item_rank, chunk_base, send_row,     \
-      send_slot, block_counter, status)
+      send_slot, block_counter, status, scales_in)
 
 void launch_dispatch_send(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers,
                           const EpMeta& m, const char* x, int row_bytes_in, bool fp8, bool cached,
                           const long long* topk_idx, const float* topk_w, const int* item_rank,
                           const int* chunk_base, int* send_row, int* send_slot,
-                          unsigned int* block_counter, int* status, int blocks, cudaStream_t st) {
+                          unsigned int* block_counter, int* status, int blocks, cudaStream_t st,
+                          const float* scales_in) {
   if (blocks < 1) blocks = 1;
   if (g.mode == 0) {
     if (fp8) { if (cached) B200EP_LAUNCH_DISPATCH(0, true, true); else B200EP_LAUNCH_DISPATCH(0, true, false); }

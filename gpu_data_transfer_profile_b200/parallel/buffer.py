@@ -316,16 +316,23 @@ class Buffer:
     def _dispatch_p1(self, x, handle, is_token_in_rank, num_tokens_per_expert, topk_idx,
                      topk_weights, use_fp8, group_by_expert, num_experts):
         R = self.group_size
+        scales_in = None
         if isinstance(x, tuple):
-            raise NotImplementedError(
-                "pre-quantised (fp8, scales) input is not supported: pass bf16 and use_fp8=True, "
-                "the cast is fused into the dispatch kernel")
+            # caller-quantised input (fp8 [T,H], f32 scales [T,H/128]): rows travel as raw bytes
+            x, scales_in = x
+            if x.dtype != torch.float8_e4m3fn or scales_in.dtype != torch.float32 or use_fp8:
+                raise ValueError("tuple input must be (float8_e4m3fn [T,H], float32 [T,H/128]) with use_fp8=False")
+            if x.shape[1] % 128 or tuple(scales_in.shape) != (x.shape[0], x.shape[1] // 128):
+                raise ValueError("scales must have shape [num_tokens, hidden/128]")
+            scales_in = scales_in.contiguous()
         if x.dim() != 2 or not x.is_contiguous():
             raise ValueError("x must be a contiguous [num_tokens, hidden] tensor")
-        if x.dtype not in _ELEM_DTYPE:
+        if x.dtype not in _ELEM_DTYPE and scales_in is None:
             raise ValueError(f"unsupported dtype {x.dtype}")
         T, H = x.shape
-        st = dict(x=x, T=T, H=H, fp8=bool(use_fp8), cached=handle is not None)
+        st = dict(x=x.view(torch.uint8) if scales_in is not None else x, T=T, H=H, fp8=bool(use_fp8),
+                  cached=handle is not None, scales_in=scales_in, fp8_out=bool(use_fp8) or scales_in is not None,
+                  in_dtype=x.dtype)
         if handle is not None:
             if handle.T != T or handle.H != H:
                 raise ValueError("cached handle does not match x")
@@ -353,8 +360,8 @@ class Buffer:
         mode, K, E = st["mode"], st["K"], st["E"]
         if E % R:
             raise ValueError("num_experts must be divisible by the group size")
-        row_bytes_out = H if st["fp8"] else H * x.element_size()
-        elem = 2 if st["fp8"] else x.element_size()
+        row_bytes_out = H if st["fp8_out"] else H * x.element_size()
+        elem = 2 if st["fp8_out"] else x.element_size()
         carve = self._get_carve(E, K, H, H * elem, H * elem)
         st["carve"] = carve
         if carve.cap <= 0:
@@ -412,7 +419,7 @@ class Buffer:
         self.C.dispatch_send(geom, regions, self.peers, st["meta"], st["x"], st["fp8"], st["cached"],
                              st["topk_idx"], st.get("topk_weights"), st.get("item_rank"),
                              st.get("chunk_hist"), st["send_row"], st["send_slot"],
-                             self.counters[1:2], self.status_ptr, self._blocks())
+                             self.counters[1:2], self.status_ptr, self._blocks(), st.get("scales_in"))
 
     def _dispatch_p3(self, st, zero_copy: bool, num_worst_tokens: int = 0):
         R, E, K, H = self.group_size, st["E"], st["K"], st["H"]
@@ -442,12 +449,12 @@ class Buffer:
         reg = dict(zip(("flags", "counts", "recv_x", "recv_scales", "recv_topk_idx", "recv_topk_w",
                         "recv_meta", "recv_prob", "comb_x", "comb_w"), st["regions"]))
         keep = (lambda t: t) if zero_copy else (lambda t: t.clone())
-        if st["fp8"]:
+        if st["fp8_out"]:
             rx = self.region.view(reg["recv_x"], (n_recv, H), "float8_e4m3fn")
             rs = self.region.view(reg["recv_scales"], (n_recv, H // 128), "float32")
             recv_x = (keep(rx), keep(rs))
         else:
-            recv_x = keep(self.region.view(reg["recv_x"], (n_recv, H), _ELEM_DTYPE[st["x"].dtype]))
+            recv_x = keep(self.region.view(reg["recv_x"], (n_recv, H), _ELEM_DTYPE[st["in_dtype"]]))
         if st["cached"]:
             return recv_x, None, None, per_expert_list, st["handle"]
         recv_topk_idx = recv_topk_w = recv_prob = None
@@ -459,7 +466,7 @@ class Buffer:
         recv_meta = self.region.view(reg["recv_meta"], (n_recv, 2), "int32").clone()
         handle = DispatchHandle(st["mode"], st["T"], H, K, E, n_recv, st["send_row"], st["send_slot"],
                                 st["meta"], recv_meta, st["topk_idx"], st.get("is_token_in_rank"),
-                                per_expert_list, st["fp8"], recv_prob)
+                                per_expert_list, st["fp8_out"], recv_prob)
         return recv_x, recv_topk_idx, recv_topk_w, per_expert_list, handle
 
     @_nvtx("b200ep.dispatch")

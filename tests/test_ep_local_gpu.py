@@ -171,3 +171,24 @@ def test_dispatch_without_host_sync_num_worst_tokens():
         buf.check_status()
     finally:
         buf.destroy()
+
+
+def test_dispatch_accepts_caller_quantised_fp8_tuple():
+    R, T, H, E, K = 2, 64, 512, 8, 2
+    xs, idxs, ws = _mk(R, T, H, E, K)
+    g = _group(R, 64 << 20)
+    try:
+        qs = [O.fp8_block_quant_ref(x) for x in xs]
+        ci, cw = [i.cuda() for i in idxs], [w.cuda() for w in ws]
+        lays = g.get_dispatch_layout(ci, E)
+        outs = g.dispatch([(q.cuda(), s.cuda()) for q, s in qs], layouts=lays, topk_idx=ci, topk_weights=cw)
+        ref_q = O.dispatch_rank_mode_ref([q.view(torch.uint8) for q, _ in qs], idxs, ws, E)
+        ref_s = O.dispatch_rank_mode_ref([s for _, s in qs], idxs, ws, E)
+        for d in range(R):
+            (rq, rs), _, _, _, h = outs[d]
+            assert rq.dtype == torch.float8_e4m3fn and h.fp8
+            assert torch.equal(rq.cpu().view(torch.uint8), ref_q[d][0])
+            assert torch.equal(rs.cpu(), ref_s[d][0])
+        g.check_status()
+    finally:
+        g.destroy()
