@@ -30,8 +30,11 @@ dispatch_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, EpMeta m,
   const int row_bytes_out = FP8 ? g.H : row_bytes_in;
   const int scale_cols = g.H / 128;
   const int gw = blockIdx.x * kSendWarps + warp, nw = gridDim.x * kSendWarps;
+  // After a notify time-out the prefix tables are not valid: store nothing (the flags below are
+  // still raised so that healthy peers are not kept waiting by this rank).
+  const int n_tokens = (!CACHED && *m.send_total < 0) ? 0 : g.T;
 
-  for (int t = gw; t < g.T; t += nw) {
+  for (int t = gw; t < n_tokens; t += nw) {
     int row = -1, slot = -1, d = 0;
     if (lane < J) {
       long long e = (MODE == 1) ? topk_idx[(size_t)t * K + lane] : 0;

@@ -207,7 +207,7 @@ __global__ void notify_wait_kernel(EpGeom g, EpRegions rg, char* self_base, EpMe
   if (!ok) {
     if (threadIdx.x == 0) {
       *m.n_recv = 0;
-      *m.send_total = 0;
+      *m.send_total = -1;      // tells dispatch_send that the offsets are not valid: send nothing
       host_word[1] = -1;
       __threadfence_system();
       host_word[0] = g.epoch;
