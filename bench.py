@@ -114,11 +114,35 @@ def main() -> int:
         out, _, _ = buf.combine(recv_x, handle)
         return out, handle
 
+    # End-to-end arm: every step copies ITS inputs from pinned host memory and reads its result
+    # back. Inputs are double-buffered on the device: the copy for step i+1 is issued on a copy
+    # stream when step i starts, so transfers overlap the previous step's kernels.
+    copy_stream = torch.cuda.Stream()
+    slots = [(torch.empty_like(x), torch.empty_like(idx), torch.empty_like(w)) for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    e2e_i = [0]
+
+    def prefetch(slot):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[slot])
+            slots[slot][0].copy_(x_h, non_blocking=True)
+            slots[slot][1].copy_(idx_h, non_blocking=True)
+            slots[slot][2].copy_(w_h, non_blocking=True)
+            ready[slot].record(copy_stream)
+
+    for ev in consumed:
+        ev.record()
+    prefetch(0)
+
     def e2e_step():
-        xd = x_h.to(dev, non_blocking=True)
-        idxd = idx_h.to(dev, non_blocking=True)
-        wd = w_h.to(dev, non_blocking=True)
-        out, _ = step(xd, idxd, wd)
+        slot = e2e_i[0] & 1
+        e2e_i[0] += 1
+        cur = torch.cuda.current_stream()
+        cur.wait_event(ready[slot])
+        prefetch(slot ^ 1)
+        out, _ = step(*slots[slot])
+        consumed[slot].record(cur)
         result_h.copy_(out.float().mean().reshape(1), non_blocking=True)
 
     flush = L2Flusher(dev)
@@ -168,7 +192,8 @@ def main() -> int:
                        "reasons": clocks["reasons"]} if clocks else None,
             "e2e": {"value": round(e2e["max_rank_mean_ms"] * 1e3, 2), "unit": "us",
                     "h2d_bytes_per_step": x_h.numel() * 2 + idx_h.numel() * 8 + w_h.numel() * 4,
-                    "d2h_bytes_per_step": 4},
+                    "d2h_bytes_per_step": 4,
+                    "pipelining": "inputs double-buffered: the H2D copy of step i+1 overlaps step i"},
             "gpu_launches": 7 * args.steps,
             "check": "ok" if ok else f"FAIL max_err={err:.4f}",
             "impl": "ours",
