@@ -20,7 +20,9 @@ combine_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, const int* __restric
                     const int2* __restrict__ recv_meta, const char* __restrict__ x, int row_bytes,
                     const float* __restrict__ topk_w, unsigned int* block_counter, int* status) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int gw = blockIdx.x * kCombWarps + warp, nw = gridDim.x * kCombWarps;
+  // slice index: consecutive slices (= neighbouring rows = same peer) land on DIFFERENT CTAs, so
+  // every SM stores to a mix of peers and local memory instead of one SM group per peer
+  const int gw = warp * gridDim.x + blockIdx.x, nw = gridDim.x * kCombWarps;
   int n = *n_recv_ptr;
   if (n > g.cap) n = g.cap;
   const int nvec = row_bytes >> 4;
