@@ -42,7 +42,10 @@ def run_one_iteration(ctx, manager, experts, args, x, fused: bool) -> IterationR
     if fused:
         buf = A.get_buffer(manager.group, A.get_hidden_bytes(x), manager.world)
         handle, manager.handle = manager.handle, None
-        out = experts.forward_fused_combine(rows, probs, buf, handle)
+        if args.backward:
+            out = experts.forward_fused_combine_train(rows, tpe, probs, buf, handle)
+        else:
+            out = experts.forward_fused_combine(rows, probs, buf, handle)
         e2.record()
     else:
         y = experts(rows, tpe, probs)
@@ -69,8 +72,6 @@ def main() -> int:
     ap.add_argument("--fuse-combine", action="store_true")
     ap.add_argument("--backward", action="store_true")
     args = ap.parse_args()
-    if args.fuse_combine and args.backward:
-        raise ValueError("--fuse-combine is a forward-only path")
     rank, world, _ = D.init_distributed()
     C.validate_args(args, world)
     group, ep_rank, _ = D.create_ep_group(args.ep)
@@ -100,7 +101,7 @@ def main() -> int:
 
     def one():
         if args.backward:
-            return run_one_iteration(ctx, manager, experts, args, x, False)
+            return run_one_iteration(ctx, manager, experts, args, x, fused and args.activation == "swiglu")
         with torch.no_grad():
             return run_one_iteration(ctx, manager, experts, args, x, fused)
 

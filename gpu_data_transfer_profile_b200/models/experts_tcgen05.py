@@ -84,6 +84,34 @@ class _GroupedMLP(torch.autograd.Function):
         return dx, dw1, dw2, dp, None, None, None
 
 
+class _GroupedMLPFusedCombine(torch.autograd.Function):
+    """Training path with the combine send fused into the fc2 GEMM epilogue: the forward returns
+    the COMBINED [T, H] tensor of this rank's tokens; the backward first dispatches the output
+    gradient with the cached handle (dispatch is combine's backward) and then runs the expert MLP
+    backward on the received rows."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2, probs, expert_off, counts, buffer, handle):
+        h = G.grouped_gemm(x, w1, expert_off)
+        act = G.swiglu_fwd(h, probs)
+        out = buffer.fused_fc2_combine(act, w2, handle)
+        ctx.save_for_backward(x, w1, w2, probs, h, act)
+        ctx.counts, ctx.off, ctx.buffer, ctx.handle = counts, expert_off, buffer, handle
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, w1, w2, probs, h, act = ctx.saved_tensors
+        dy, *_ = ctx.buffer.dispatch(grad_out.contiguous(), handle=ctx.handle)
+        rows = sum(ctx.counts)
+        dact = G.grouped_gemm(dy, w2.transpose(1, 2).contiguous(), ctx.off)
+        dh, dp = G.swiglu_bwd(h, probs, dact)
+        dx = G.grouped_gemm(dh, w1.transpose(1, 2).contiguous(), ctx.off)
+        dw2 = _wgrad(dy[:rows], act[:rows], ctx.counts, w2.shape)
+        dw1 = _wgrad(dh[:rows], x[:rows], ctx.counts, w1.shape)
+        return dx, dw1, dw2, dp, None, None, None, None
+
+
 class Tcgen05GroupedExperts(GroupedExpertsBase):
     def __init__(self, num_local_experts, hidden_size, ffn_hidden_size, dtype=torch.bfloat16,
                  activation="swiglu", device="cuda", init_std: float = 0.02):
@@ -104,6 +132,16 @@ class Tcgen05GroupedExperts(GroupedExpertsBase):
         counts, off = self._offsets(tokens_per_expert, hidden_states.device, expert_off)
         return _GroupedMLP.apply(hidden_states.contiguous(), self.weight1, self.weight2,
                                  routed_probs.float().contiguous(), off, counts, self.activation)
+
+    def forward_fused_combine_train(self, hidden_states, tokens_per_expert, routed_probs, buffer, handle):
+        """Differentiable twin of `forward_fused_combine` (SwiGLU only)."""
+        if self.activation != "swiglu":
+            raise ValueError("the fused training path supports swiglu")
+        El = self.num_local_experts
+        counts = [int(v) for v in (tokens_per_expert.tolist() if torch.is_tensor(tokens_per_expert) else tokens_per_expert)]
+        off = handle.meta[2 + El: 2 + El + El + 1]
+        return _GroupedMLPFusedCombine.apply(hidden_states.contiguous(), self.weight1, self.weight2,
+                                             routed_probs.float().contiguous(), off, counts, buffer, handle)
 
     @torch.no_grad()
     def forward_fused_combine(self, hidden_states, routed_probs, buffer, handle):

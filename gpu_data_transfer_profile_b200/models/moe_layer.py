@@ -46,13 +46,15 @@ class MoELayer(torch.nn.Module):
             router_logits = self.router(hidden_states.float())
         idx, probs = topk_softmax_router(router_logits, self.topk)
         rows, tokens_per_expert, row_probs = self.dispatcher.dispatch(hidden_states, idx, probs)
-        if (self.fuse_combine and not torch.is_grad_enabled() and self.dispatcher.mode == "fused"
-                and hasattr(self.experts, "forward_fused_combine")):
-            # forward-only fast path: the fc2 epilogue stores straight into the source ranks' slots
+        if (self.fuse_combine and self.dispatcher.mode == "fused" and hasattr(self.experts, "forward_fused_combine")
+                and (not torch.is_grad_enabled() or self.experts.activation == "swiglu")):
+            # the fc2 epilogue stores straight into the source ranks' slots (no combine-send kernel)
             from . import fused_a2a as A
             buf = A.get_buffer(self.dispatcher.group, A.get_hidden_bytes(hidden_states), self.dispatcher.world)
             handle = self.dispatcher.handle
             self.dispatcher.handle = None
+            if torch.is_grad_enabled():
+                return self.experts.forward_fused_combine_train(rows, tokens_per_expert, row_probs, buf, handle)
             return self.experts.forward_fused_combine(rows, row_probs, buf, handle)
         out_rows = self.experts(rows, tokens_per_expert, row_probs)
         return self.dispatcher.combine(out_rows)

@@ -47,6 +47,37 @@ def test_moe_layer_forward_backward_matches_dense_oracle(mode, activation):
         A.release_buffers()
 
 
+def test_moe_layer_fused_combine_training_path_gradients():
+    """fc2 epilogue performs the combine send in the TRAINING forward; gradients must equal the
+    separate-combine path."""
+    from gpu_data_transfer_profile_b200.models import fused_a2a as A
+    from gpu_data_transfer_profile_b200.models.moe_layer import MoELayer
+    from gpu_data_transfer_profile_b200.parallel.symm import LocalWorld
+    torch.manual_seed(0)
+    T, H, F, E, K = 200, 256, 512, 4, 2
+    world = LocalWorld.make(1)[0]
+    A.configure_buffer(num_max_tokens_per_rank=256, num_topk=K, num_experts=E, group_by_expert=True)
+    try:
+        layer = MoELayer(H, F, E, K, None, dtype=torch.bfloat16, expert_backend="tcgen05", world=world)
+        x0 = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        logits = torch.randn(T, E, device="cuda")
+        g = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        res = []
+        for fuse in (True, False):
+            layer.fuse_combine = fuse
+            layer.zero_grad()
+            x = x0.clone().requires_grad_(True)
+            lg = logits.clone().requires_grad_(True)
+            out = layer(x, lg)
+            out.backward(g)
+            res.append((out.detach().float(), x.grad.float(), lg.grad.float(), layer.experts.weight1.grad.float().clone(),
+                        layer.experts.weight2.grad.float().clone()))
+        for a, b in zip(*res):
+            torch.testing.assert_close(a, b, atol=3e-2, rtol=3e-2)
+    finally:
+        A.release_buffers()
+
+
 @pytest.mark.parametrize("fused", [False, True])
 def test_moe_layer_tcgen05_experts_bf16(fused):
     """bf16 layer on the tcgen05 grouped GEMMs (separate combine with autograd, and the forward-only
