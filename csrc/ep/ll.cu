@@ -19,11 +19,43 @@ namespace b200ep {
 
 constexpr int kLLThreads = 256;  // 8 warps work on one row together
 
-__device__ __forceinline__ int block_epoch(const int* epoch_ptr, int add) {
-  __shared__ int s_epoch;
-  if (threadIdx.x == 0) s_epoch = *reinterpret_cast<const volatile int*>(epoch_ptr) + add;
+// Per-op device state (4 ints): [0] committed epoch, [1] committed arrival target,
+// [2] epoch published by the send half, [3] target published by the send half.
+// Send half: works with epoch = [0]+1, target = [1]+grid; CTA 0 publishes them in [2],[3].
+// Receive half (next launch on the stream): reads [2],[3]; CTA 0 commits them to [0],[1].
+// No kernel ever reads a word that another CTA of the same launch writes.
+struct LLTick { int epoch, target; };
+
+__device__ __forceinline__ LLTick ll_tick_send(int* st, int grid_ctas) {
+  __shared__ int s_e, s_t;
+  if (threadIdx.x == 0) {
+    s_e = *reinterpret_cast<volatile int*>(st + 0) + 1;
+    s_t = *reinterpret_cast<volatile int*>(st + 1) + grid_ctas;
+    if (blockIdx.x == 0 && blockIdx.y == 0) { st[2] = s_e; st[3] = s_t; }
+  }
   __syncthreads();
-  return s_epoch;
+  return LLTick{s_e, s_t};
+}
+__device__ __forceinline__ LLTick ll_tick_recv(int* st) {
+  __shared__ int s_e, s_t;
+  if (threadIdx.x == 0) {
+    s_e = *reinterpret_cast<volatile int*>(st + 2);
+    s_t = *reinterpret_cast<volatile int*>(st + 3);
+    if (blockIdx.x == 0 && blockIdx.y == 0) { st[0] = s_e; st[1] = s_t; }
+  }
+  __syncthreads();
+  return LLTick{s_e, s_t};
+}
+// Every CTA of a send kernel ends with this: its stores become visible system-wide, then it
+// adds 1 to this rank's arrival counter on every peer. A receiver waits for counter >= target,
+// i.e. for ALL CTAs of that sender (the grid size is the same on every rank), so no CTA has to
+// wait for the others and no second fence follows a "last block".
+__device__ __forceinline__ void ll_arrive_on_peers(const LLParams& P, const PeerPtrs& peers, int channel) {
+  __syncthreads();
+  if (threadIdx.x < P.R) {
+    unsigned int* ctr = reinterpret_cast<unsigned int*>(peers.base[threadIdx.x] + P.flags) + channel * kMaxRanks + P.rank;
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -31,13 +63,17 @@ __device__ __forceinline__ int block_epoch(const int* epoch_ptr, int add) {
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kLLThreads)
 ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
-                        const long long* __restrict__ topk_idx, int* send_cnt, int* epoch_ptr,
-                        unsigned int* block_counter, int* status) {
+                        const long long* __restrict__ topk_idx, int* send_cnt_all, int* state,
+                        int* status) {
   __shared__ char* s_dst[kMaxItemsPerToken];
   __shared__ float* s_scl[kMaxItemsPerToken];
   __shared__ int s_n;
-  const int epoch = block_epoch(epoch_ptr, 1);
+  const LLTick tk = ll_tick_send(state, gridDim.x);
+  const int epoch = tk.epoch;
   const int par = epoch & 1;
+  int* send_cnt = send_cnt_all + par * P.E;            // slot counters of this epoch (zero on entry)
+  if (blockIdx.x == 0)                                   // ... and clear the other set for the next call
+    for (int e = threadIdx.x; e < P.E; e += kLLThreads) send_cnt_all[(par ^ 1) * P.E + e] = 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kLLThreads / 32;
   const int row_bytes = P.fp8 ? P.H : P.H * 2;
   const int scale_cols = P.H / 128;
@@ -53,6 +89,7 @@ ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
           const size_t row = ((size_t)el * P.R + P.rank) * P.M + slot;
           char* pb = peers.base[d];
           reinterpret_cast<int*>(pb + P.recv_src[par])[row] = (t << 5) | (int)threadIdx.x;
+          reinterpret_cast<int*>(pb + P.recv_tag[par])[row] = epoch;      // marks the slot as written in this epoch
           const int i = atomicAdd(&s_n, 1);
           s_dst[i] = pb + P.recv_x[par] + row * row_bytes;
           s_scl[i] = reinterpret_cast<float*>(pb + P.recv_scales[par]) + row * scale_cols;
@@ -110,20 +147,7 @@ ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
     }
     __syncthreads();
   }
-  if (!last_block_arrive(block_counter, gridDim.x)) return;
-  // last CTA: publish my per-expert counts to the owners, reset them, raise the flags.
-  for (int e = threadIdx.x; e < P.E; e += kLLThreads) {
-    const int c = min(*reinterpret_cast<volatile int*>(&send_cnt[e]), P.M);
-    send_cnt[e] = 0;
-    int* dst = reinterpret_cast<int*>(peers.base[e / P.El] + P.count[par]) + (e % P.El) * P.R + P.rank;
-    st_relaxed_sys(dst, c);
-  }
-  __syncthreads();   // the flag stores below are system-scope releases, cumulative over the CTA's stores
-  if (threadIdx.x < P.R) {
-    int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + P.flags) + kChLLDispatch * kMaxRanks + P.rank;
-    st_release_sys(flag, epoch);
-  }
-  if (threadIdx.x == 0) *epoch_ptr = epoch;
+  ll_arrive_on_peers(P, peers, kChLLDispatch);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -134,16 +158,19 @@ __global__ void __launch_bounds__(kLLThreads)
 ll_dispatch_recv_kernel(LLParams P, char* self_base, char* __restrict__ out_x,
                         float* __restrict__ out_scales, int* __restrict__ out_src,
                         int* __restrict__ out_count, int2* __restrict__ out_range,
-                        const int* epoch_ptr, int* status) {
+                        int* state, int* status) {
   __shared__ int s_off[kMaxRanks + 1];
+  __shared__ int s_cnt[kMaxRanks];
   __shared__ int ok;
-  const int epoch = block_epoch(epoch_ptr, 0);
+  const LLTick tk = ll_tick_recv(state);
+  const int epoch = tk.epoch;
   const int par = epoch & 1;
   if (threadIdx.x == 0) ok = 1;
+  if (threadIdx.x < kMaxRanks) s_cnt[threadIdx.x] = 0;
   __syncthreads();
   if (threadIdx.x < P.R) {
     const int* flags = reinterpret_cast<const int*>(self_base + P.flags) + kChLLDispatch * kMaxRanks;
-    if (!wait_flag_ge(flags + threadIdx.x, epoch, P.timeout_ns, status, kTimeoutLowLatency)) ok = 0;
+    if (!wait_flag_ge(flags + threadIdx.x, tk.target, P.timeout_ns, status, kTimeoutLowLatency)) ok = 0;
   }
   __syncthreads();
   const int el = blockIdx.x;
@@ -151,12 +178,16 @@ ll_dispatch_recv_kernel(LLParams P, char* self_base, char* __restrict__ out_x,
     if (threadIdx.x == 0 && blockIdx.y == 0) out_count[el] = 0;
     return;
   }
-  const int* cnt = reinterpret_cast<const int*>(self_base + P.count[par]) + el * P.R;
+  // rows of (el, source s) occupy slots 0..count-1; a slot belongs to this call iff its tag is the epoch
+  const int* tags = reinterpret_cast<const int*>(self_base + P.recv_tag[par]) + (size_t)el * P.R * P.M;
+  for (int i = threadIdx.x; i < P.R * P.M; i += kLLThreads)
+    if (__ldcg(&tags[i]) == epoch) atomicAdd(&s_cnt[i / P.M], 1);
+  __syncthreads();
   if (threadIdx.x == 0) {
     int acc = 0;
     for (int s = 0; s < P.R; ++s) {
       s_off[s] = acc;
-      int c = __ldcg(&cnt[s]);
+      int c = s_cnt[s];
       c = c < 0 ? 0 : (c > P.M ? P.M : c);
       if (blockIdx.y == 0) out_range[el * P.R + s] = make_int2(acc, c);
       acc += c;
@@ -204,9 +235,9 @@ ll_dispatch_recv_kernel(LLParams P, char* self_base, char* __restrict__ out_x,
 __global__ void __launch_bounds__(kLLThreads)
 ll_combine_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
                        const int* __restrict__ src_info, const int* __restrict__ count,
-                       int* epoch_ptr, unsigned int* block_counter, int* status) {
-  const int epoch = block_epoch(epoch_ptr, 1);
-  const int par = epoch & 1;
+                       int* state, int* status) {
+  const LLTick tk = ll_tick_send(state, gridDim.x * gridDim.y);
+  const int par = tk.epoch & 1;
   const int el = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kLLThreads / 32;
   const size_t cap = (size_t)P.R * P.M;
@@ -239,28 +270,23 @@ ll_combine_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
         if (v0 + u * 32 < nv) st_global_v4(dst + ((size_t)(v0 + u * 32) << 4), buf[u]);
     }
   }
-  if (!last_block_arrive(block_counter, gridDim.x * gridDim.y)) return;
-  if (threadIdx.x < P.R) {
-    int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + P.flags) + kChLLCombine * kMaxRanks + P.rank;
-    st_release_sys(flag, epoch);
-  }
-  if (threadIdx.x == 0) *epoch_ptr = epoch;
+  ll_arrive_on_peers(P, peers, kChLLCombine);
 }
 
 // combine, receive half: out[t] = sum_k w[t,k] * slot(t,k) over k with topk_idx[t,k] >= 0.
 __global__ void __launch_bounds__(kLLThreads)
 ll_combine_recv_kernel(LLParams P, char* self_base, const long long* __restrict__ topk_idx,
                        const float* __restrict__ topk_w, char* __restrict__ out,
-                       const int* epoch_ptr, int* status) {
+                       int* state, int* status) {
   __shared__ float s_w[kMaxItemsPerToken];
   __shared__ int ok;
-  const int epoch = block_epoch(epoch_ptr, 0);
-  const int par = epoch & 1;
+  const LLTick tk = ll_tick_recv(state);
+  const int par = tk.epoch & 1;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
   if (threadIdx.x < P.R) {
     const int* flags = reinterpret_cast<const int*>(self_base + P.flags) + kChLLCombine * kMaxRanks;
-    if (!wait_flag_ge(flags + threadIdx.x, epoch, P.timeout_ns, status, kTimeoutLowLatency)) ok = 0;
+    if (!wait_flag_ge(flags + threadIdx.x, tk.target, P.timeout_ns, status, kTimeoutLowLatency)) ok = 0;
   }
   __syncthreads();
   if (!ok) return;
@@ -305,33 +331,30 @@ ll_combine_recv_kernel(LLParams P, char* self_base, const long long* __restrict_
 }
 
 // ---- launchers -------------------------------------------------------------------------
+// The dispatch send grid is ALWAYS P.G CTAs and the combine send grid ALWAYS (El, P.Gc / El):
+// receivers count arrivals, so the number of CTAs must be the same on every rank.
 void launch_ll_dispatch_send(const LLParams& P, const PeerPtrs& peers, const char* x,
-                             const long long* topk_idx, int* send_cnt, int* epoch_ptr,
-                             unsigned int* counter, int* status, int blocks, cudaStream_t st) {
-  int g = P.T < blocks ? P.T : blocks;
-  if (g < 1) g = 1;
-  ll_dispatch_send_kernel<<<g, kLLThreads, 0, st>>>(P, peers, x, topk_idx, send_cnt, epoch_ptr, counter, status);
+                             const long long* topk_idx, int* send_cnt, int* state, int* status,
+                             cudaStream_t st) {
+  ll_dispatch_send_kernel<<<P.G, kLLThreads, 0, st>>>(P, peers, x, topk_idx, send_cnt, state, status);
 }
 void launch_ll_dispatch_recv(const LLParams& P, char* self_base, char* out_x, float* out_scales,
-                             int* out_src, int* out_count, int* out_range, const int* epoch_ptr,
+                             int* out_src, int* out_count, int* out_range, int* state,
                              int* status, int split, cudaStream_t st) {
   if (split < 1) split = 1;
   ll_dispatch_recv_kernel<<<dim3(P.El, split), kLLThreads, 0, st>>>(
-      P, self_base, out_x, out_scales, out_src, out_count, reinterpret_cast<int2*>(out_range), epoch_ptr, status);
+      P, self_base, out_x, out_scales, out_src, out_count, reinterpret_cast<int2*>(out_range), state, status);
 }
 void launch_ll_combine_send(const LLParams& P, const PeerPtrs& peers, const char* x, const int* src_info,
-                            const int* count, int* epoch_ptr, unsigned int* counter, int* status,
-                            int split, cudaStream_t st) {
-  if (split < 1) split = 1;
-  ll_combine_send_kernel<<<dim3(P.El, split), kLLThreads, 0, st>>>(P, peers, x, src_info, count, epoch_ptr,
-                                                                   counter, status);
+                            const int* count, int* state, int* status, cudaStream_t st) {
+  ll_combine_send_kernel<<<dim3(P.El, P.Gc / P.El), kLLThreads, 0, st>>>(P, peers, x, src_info, count, state, status);
 }
 void launch_ll_combine_recv(const LLParams& P, char* self_base, const long long* topk_idx,
-                            const float* topk_w, char* out, const int* epoch_ptr, int* status,
+                            const float* topk_w, char* out, int* state, int* status,
                             int blocks, cudaStream_t st) {
   int g = P.T < blocks ? P.T : blocks;
   if (g < 1) g = 1;
-  ll_combine_recv_kernel<<<g, kLLThreads, 0, st>>>(P, self_base, topk_idx, topk_w, out, epoch_ptr, status);
+  ll_combine_recv_kernel<<<g, kLLThreads, 0, st>>>(P, self_base, topk_idx, topk_w, out, state, status);
 }
 
 }  // namespace b200ep

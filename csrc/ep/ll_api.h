@@ -16,20 +16,23 @@ struct LLParams {
   long long recv_scales[2];   // float [El][R][M][H/128]
   long long recv_src[2];      // int [El][R][M]  (token << 5 | k)
   long long comb_x[2];        // bf16 [M][K][H]
+  long long recv_tag[2];      // int [El][R][M]  epoch in which the slot was written
+  int G;                      // CTAs of EVERY dispatch-send launch (same on all ranks)
+  int Gc;                     // CTAs of EVERY combine-send launch (multiple of El)
   unsigned long long timeout_ns;
 };
 
+// `state`: device int[4] per op (see ll.cu). `send_cnt`: device int[2*E], zero-initialised once.
 void launch_ll_dispatch_send(const LLParams& P, const PeerPtrs& peers, const char* x,
-                             const long long* topk_idx, int* send_cnt, int* epoch_ptr,
-                             unsigned int* counter, int* status, int blocks, cudaStream_t st);
+                             const long long* topk_idx, int* send_cnt, int* state, int* status,
+                             cudaStream_t st);
 void launch_ll_dispatch_recv(const LLParams& P, char* self_base, char* out_x, float* out_scales,
-                             int* out_src, int* out_count, int* out_range, const int* epoch_ptr,
+                             int* out_src, int* out_count, int* out_range, int* state,
                              int* status, int split, cudaStream_t st);
 void launch_ll_combine_send(const LLParams& P, const PeerPtrs& peers, const char* x, const int* src_info,
-                            const int* count, int* epoch_ptr, unsigned int* counter, int* status,
-                            int split, cudaStream_t st);
+                            const int* count, int* state, int* status, cudaStream_t st);
 void launch_ll_combine_recv(const LLParams& P, char* self_base, const long long* topk_idx,
-                            const float* topk_w, char* out, const int* epoch_ptr, int* status,
+                            const float* topk_w, char* out, int* state, int* status,
                             int blocks, cudaStream_t st);
 
 }  // namespace b200ep

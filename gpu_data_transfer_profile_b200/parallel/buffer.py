@@ -188,6 +188,7 @@ class Buffer:
         self._epoch = dict(notify=0, dispatch=0, combine=0, barrier=0, ll_dispatch=0, ll_combine=0)
         self._carve: Optional[_Carve] = None
         self._ll = None
+        self._ll_words = None
         self.world.host_barrier()
 
     def destroy(self):
@@ -566,17 +567,28 @@ class Buffer:
                                  num_experts: int = 0) -> None:
         """Nothing to clean: flags are epochs and regions are double-buffered."""
 
+    LL_SPLIT = 4          # combine-send CTAs per local expert
+
     def _ll_state(self, E: int, K: int, H: int, M: int):
         key = (E, K, H, M)
         if self._ll is None or self._ll["key"] != key:
-            if self._ll is not None or self._carve is not None:
-                self.barrier()
+            reuse = self._ll is not None or self._carve is not None
             carve = _LLCarve(self.num_nvl_bytes, self.group_size, E, M, H, K)
             dev = self.device
-            self._ll = dict(key=key, carve=carve,
-                            epochs=torch.zeros(2, dtype=torch.int32, device=dev),
-                            send_cnt=torch.zeros(E, dtype=torch.int32, device=dev),
-                            counters=torch.zeros(2, dtype=torch.int32, device=dev))
+            if reuse:
+                # the region held other data: every rank drains, clears its slot tags (a stale word
+                # must never look like a current epoch), and only then may anyone send again
+                self.barrier()
+                rows = (E // self.group_size) * self.group_size * M
+                for off in carve.recv_tag:
+                    self.region.view(off, (rows,), "int32").zero_()
+                self.barrier()
+            if self._ll_words is None:
+                # device-resident op state (epochs and arrival targets); lives as long as the buffer
+                # because the peers' arrival counters are cumulative
+                self._ll_words = torch.zeros(8, dtype=torch.int32, device=dev)
+            self._ll = dict(key=key, carve=carve, words=self._ll_words,
+                            send_cnt=torch.zeros(2 * E, dtype=torch.int32, device=dev))
             self._carve = None
         return self._ll
 
@@ -584,8 +596,9 @@ class Buffer:
         E, K, H, M = st["key"]
         c = st["carve"]
         R = self.group_size
-        return [self.rank, R, E, E // R, K, H, M, T, int(fp8), 0, *c.count, *c.recv_x, *c.recv_scales,
-                *c.recv_src, *c.comb_x, self._timeout_ns()]
+        El = E // R
+        return [self.rank, R, E, El, K, H, M, T, int(fp8), 0, *c.count, *c.recv_x, *c.recv_scales,
+                *c.recv_src, *c.comb_x, self._timeout_ns(), *c.recv_tag, min(M, 128), El * Buffer.LL_SPLIT]
 
     def _ll_dispatch_send(self, x, topk_idx, M, E, use_fp8):
         if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
@@ -599,8 +612,7 @@ class Buffer:
         K = topk_idx.shape[1]
         st = self._ll_state(E, K, H, M)
         pv = self._ll_params(st, T, use_fp8)
-        self.C.ll_dispatch_send(pv, self.peers, x, topk_idx, st["send_cnt"], st["epochs"][0:1],
-                                st["counters"][0:1], self.status_ptr, max(Buffer.num_sms * 4, 1))
+        self.C.ll_dispatch_send(pv, self.peers, x, topk_idx, st["send_cnt"], st["words"][0:4], self.status_ptr)
         return dict(st=st, pv=pv, T=T, H=H, K=K, E=E, M=M, fp8=use_fp8, topk_idx=topk_idx, x=x)
 
     def _ll_dispatch_recv(self, d):
@@ -617,7 +629,7 @@ class Buffer:
         out_count = torch.empty((El,), dtype=torch.int32, device=dev)
         out_range = torch.empty((El, R, 2), dtype=torch.int32, device=dev)
         self.C.ll_dispatch_recv(d["pv"], self.region.local_ptr, out_x, out_s, out_src, out_count, out_range,
-                                d["st"]["epochs"][0:1], self.status_ptr, 4)
+                                d["st"]["words"][0:4], self.status_ptr, 4)
         handle = (out_src, out_range, M, H, d["E"], out_count, d["K"])
         return ((out_x, out_s) if d["fp8"] else out_x), out_count, handle
 
@@ -652,8 +664,7 @@ class Buffer:
         if x.dtype != torch.bfloat16 or not x.is_contiguous():
             raise ValueError("low-latency combine takes a contiguous bf16 [E_local, R*M, hidden] tensor")
         pv = self._ll_params(st, 0, False)
-        self.C.ll_combine_send(pv, self.peers, x, src_info, count, st["epochs"][1:2], st["counters"][1:2],
-                               self.status_ptr, 4)
+        self.C.ll_combine_send(pv, self.peers, x, src_info, count, st["words"][4:8], self.status_ptr)
         return dict(st=st, H=H)
 
     def _ll_combine_recv(self, c, topk_idx, topk_weights, out=None):
@@ -663,7 +674,7 @@ class Buffer:
         if out is None:
             out = torch.empty((T, c["H"]), dtype=torch.bfloat16, device=self.device)
         w = topk_weights.to(torch.float32).contiguous() if topk_weights is not None else None
-        self.C.ll_combine_recv(pv, self.region.local_ptr, topk_idx, w, out, c["st"]["epochs"][1:2],
+        self.C.ll_combine_recv(pv, self.region.local_ptr, topk_idx, w, out, c["st"]["words"][4:8],
                                self.status_ptr, max(Buffer.num_sms * 4, 1))
         return out
 
@@ -691,7 +702,7 @@ class _LLCarve:
         El = E // R
         rows = El * R * M
         return dict(recv_x=rows * H * 2, recv_scales=rows * max(H // 128, 1) * 4, recv_src=rows * 4,
-                    comb_x=M * K * H * 2)
+                    recv_tag=rows * 4, comb_x=M * K * H * 2)
 
     @staticmethod
     def required_bytes(R, E, M, H, K) -> int:

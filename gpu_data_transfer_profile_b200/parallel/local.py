@@ -47,6 +47,8 @@ class LocalGroup:
                 for r, b in enumerate(self.buffers)]
 
     def low_latency_dispatch(self, xs, topk_idx, num_max_tokens: int, num_experts: int, use_fp8=True):
+        for r, b in enumerate(self.buffers):     # every virtual rank prepares its regions before anyone sends
+            b._ll_state(num_experts, topk_idx[r].shape[1], xs[r].shape[1], num_max_tokens)
         ds = [b._ll_dispatch_send(xs[r], topk_idx[r], num_max_tokens, num_experts, use_fp8)
               for r, b in enumerate(self.buffers)]
         return [b._ll_dispatch_recv(ds[r]) for r, b in enumerate(self.buffers)]
