@@ -14,6 +14,7 @@ struct GemmParams {
   int N_out;              // columns of the stored result (== N)
   int w_rows;             // rows per expert in the weight tensor (N, or 2F for swiglu)
   int n_tiles, max_rows;  // filled by the launcher
+  int band_rows;          // activation rows per L2-resident band of the tile order (<= 0: 2048)
   const int* expert_off;  // device [El+1]: exclusive prefix of rows per local expert
   void* out;              // bf16 [rows, out_ld]           (plain / swiglu)
   long long out_ld;
@@ -28,8 +29,10 @@ struct GemmParams {
 };
 
 // a: bf16 [a_rows, K] on this GPU; w: bf16 [El * w_rows, K] on this GPU. Returns 0 on success.
+// pair: run CTA pairs (clusters of two SMs, `cta_group::2`) on 256 x 256 tiles instead of single
+// CTAs on 128 x 256 tiles; `ctas` then counts CTAs as well (pairs = ctas / 2, capped by residency).
 int launch_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, GemmParams p,
-                        const PeerPtrs& peers, int ctas, cudaStream_t st);
+                        const PeerPtrs& peers, int ctas, bool pair, cudaStream_t st);
 
 // SwiGLU x prob elementwise pair for the training path (h: bf16 [rows, 2F], gate columns first).
 // n_rows_ptr (device, optional) bounds the rows actually processed; max_rows is the tensor's size.

@@ -13,9 +13,15 @@
 //                 line), so no separate unpermute/combine-send kernel runs; the source reduces
 //                 its slots on arrival (combine_reduce_kernel).
 // Structure: persistent CTAs, one per SM; warp 0 = TMA producer (plain tile loads of this
-// GPU's memory, no cluster multicast), warp 1 = MMA issuer and TMEM owner, warps 2-5 = epilogue.
-// 4-stage smem ring (A 128x64 + B 256x64 bf16, 128-byte swizzle), 2 TMEM accumulators
-// (128 lanes x 256 f32 columns each) so the epilogue of tile i overlaps the MMAs of tile i+1.
+// GPU's memory; every CTA fetches its own tiles), warp 1 = MMA issuer and TMEM owner,
+// warps 2-5 = epilogue. 2 TMEM accumulators (128 lanes x 256 f32 columns each) so the epilogue
+// of tile i overlaps the MMAs of tile i+1. Two forms of the same kernel (template CG):
+//   CG = 1: one CTA per 128 x 256 tile; 4-stage ring of A 128x64 + B 256x64 (bf16, 128-byte swizzle).
+//   CG = 2: a CTA pair (cluster of two SMs, `cta_group::2`) per 256 x 256 tile. Each CTA loads
+//           its own 128 rows of A and HALF of the weight tile (128 of the 256 weight rows); the
+//           leader CTA issues one MMA that reads both halves from the two CTAs' shared memory and
+//           writes 128 accumulator lanes into each CTA's TMEM. A weight tile is thus fetched once
+//           per pair and the shared-memory traffic per flop halves for B; 6-stage ring of 32 KiB.
 // The tile list is derived on the device from the per-expert row offsets (no host sync).
 // Every mbarrier wait is bounded; on a time-out all roles leave their loops, TMEM is freed.
 #include <cuda_bf16.h>
@@ -26,55 +32,78 @@ namespace b200ep {
 
 using namespace tc;
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2, B_HALF_BYTES = 128 * BK * 2, STAGE_BYTES = A_BYTES + 2 * B_HALF_BYTES;
+constexpr int BM = 128, BN = 256, BK = 64;                    // BM: rows per CTA
+constexpr int A_BYTES = BM * BK * 2, B_HALF_BYTES = 128 * BK * 2;
+// per-CTA stage: A tile + the part of the weight tile this CTA holds (all of it, or one half)
+template <int CG> struct Ring;
+template <> struct Ring<1> { static constexpr int STAGES = 4, STAGE_BYTES = A_BYTES + 2 * B_HALF_BYTES; };
+template <> struct Ring<2> { static constexpr int STAGES = 6, STAGE_BYTES = A_BYTES + B_HALF_BYTES; };
+constexpr int MAX_STAGES = 6;
 constexpr int EPI_ROW_BYTES = 128 + 16;                       // 64 bf16 + pad (bank spread)
 constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * EPI_WARP_BYTES + 1024 /*align slack*/;
+constexpr int RING_BYTES = 4 * (A_BYTES + 2 * B_HALF_BYTES);
+static_assert(Ring<1>::STAGES * Ring<1>::STAGE_BYTES == RING_BYTES && Ring<2>::STAGES * Ring<2>::STAGE_BYTES == RING_BYTES, "");
+constexpr int SMEM_BYTES = RING_BYTES + 4 * EPI_WARP_BYTES + 1024 /*align slack*/;
 constexpr int GEMM_THREADS = 192;
 constexpr int kMaxLocalExperts = 256;
 
 struct Tile { int e, row0, valid_rows, nt; };
 
-// Tile t -> (expert, first row, valid rows, n-tile). Tiles of one expert are consecutive,
-// m fastest, so CTAs that run together share the same weight tile in L2.
+// Tile t -> (expert, first row, valid rows, n-tile) as seen by the calling CTA. A tile spans
+// TM = 128 * CG rows; CTA `cta_rank` of a pair owns rows [128 * cta_rank, +128) of it (possibly
+// none of them valid). Order inside one expert: bands of `gm` m-tiles; inside a band m runs
+// fastest, then n, so the tiles in flight at one time cover a band of activation rows times a
+// few weight tiles, the band stays in L2 while all weight tiles pass over it, and an expert
+// whose activations exceed L2 is not re-read from HBM once per weight tile.
+template <int TM>
 __device__ __forceinline__ bool decode_tile(int t, const int* s_tile_off, const int* s_row_off, int El,
-                                            int n_tiles, Tile& out) {
+                                            int n_tiles, int gm, int cta_rank, Tile& out) {
   if (t >= s_tile_off[El]) return false;
   int e = 0;
   while (e + 1 < El && t >= s_tile_off[e + 1]) ++e;
   const int local = t - s_tile_off[e];
   const int rows = s_row_off[e + 1] - s_row_off[e];
-  const int m_tiles = (rows + BM - 1) / BM;
-  const int mt = local % m_tiles;
+  const int m_tiles = (rows + TM - 1) / TM;
+  const int per_band = gm * n_tiles;
+  const int band = local / per_band;
+  const int idx = local - band * per_band;
+  const int band_m = min(gm, m_tiles - band * gm);
+  const int mt = band * gm + idx % band_m;
   out.e = e;
-  out.nt = local / m_tiles;
-  out.row0 = s_row_off[e] + mt * BM;
-  out.valid_rows = min(BM, rows - mt * BM);
-  (void)n_tiles;
+  out.nt = idx / band_m;
+  out.row0 = s_row_off[e] + mt * TM + cta_rank * BM;
+  out.valid_rows = max(0, min(BM, rows - mt * TM - cta_rank * BM));
   return true;
 }
 
 __device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
 
-template <int EPI>
+template <int EPI, int CG>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ GemmParams p, const __grid_constant__ PeerPtrs peers) {
+  constexpr int STAGES = Ring<CG>::STAGES, STAGE_BYTES = Ring<CG>::STAGE_BYTES, TM = BM * CG;
   extern __shared__ unsigned char smem_raw[];
-  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_tile_off[kMaxLocalExperts + 1], s_row_off[kMaxLocalExperts + 1];
 
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* epi_smem = smem + STAGES * STAGE_BYTES;
+  unsigned char* epi_smem = smem + RING_BYTES;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort = &s_abort;
+  // work unit = CTA (CG 1) or CTA pair (CG 2); in a pair, rank 0 leads: it owns the barriers the
+  // MMA thread waits on and issues every MMA; both CTAs load, both run an epilogue on their own TMEM
+  const int cta_rank = CG == 2 ? (int)cluster_cta_rank() : 0;
+  const bool leader = cta_rank == 0;
+  const int unit = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int n_units = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int gm = max(1, p.band_rows / TM);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4 * CG); }
     s_abort = 0;
     fence_barrier_init();
     // device-side tile table: rows per expert come from the dispatch metadata
@@ -86,15 +115,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       s_row_off[e] = r0;
       s_row_off[e + 1] = r1;
       s_tile_off[e] = acc;
-      acc += ((r1 - r0 + BM - 1) / BM) * p.n_tiles;
+      acc += ((r1 - r0 + TM - 1) / TM) * p.n_tiles;
     }
     s_tile_off[p.El] = acc;
     prefetch_tmap(&map_a);
     prefetch_tmap(&map_b);
   }
-  if (warp == 1) tmem_alloc(&s_tmem, 512);
+  if (warp == 1) {
+    if (CG == 2) tmem_alloc_pair(&s_tmem, 512); else tmem_alloc(&s_tmem, 512);
+  }
   fence_before_sync();
   __syncthreads();
+  __syncwarp();
+  if (CG == 2) cluster_sync_all();      // the peer's barriers are initialised before anything arrives on them
   fence_after_sync();
   const uint32_t tmem_base = s_tmem;
   const int k_blocks = (p.K + BK - 1) / BK;
@@ -104,34 +137,50 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (elect_one()) {
       uint32_t it = 0;
       Tile tl;
-      for (int t = blockIdx.x; decode_tile(t, s_tile_off, s_row_off, p.El, p.n_tiles, tl) && !*abort; t += gridDim.x) {
-        const int b_row0 = (EPI == EPI_SWIGLU) ? tl.e * p.w_rows + tl.nt * 128 : tl.e * p.w_rows + tl.nt * BN;
-        const int b_row1 = (EPI == EPI_SWIGLU) ? b_row0 + p.N : b_row0 + 128;
+      for (int t = unit; decode_tile<TM>(t, s_tile_off, s_row_off, p.El, p.n_tiles, gm, cta_rank, tl) && !*abort; t += n_units) {
+        // weight rows of this tile: [gate 128 | linear 128] for swiglu, 256 consecutive rows otherwise;
+        // one CTA loads both halves, a pair splits them
+        const int b_first = (EPI == EPI_SWIGLU) ? tl.e * p.w_rows + tl.nt * 128 : tl.e * p.w_rows + tl.nt * BN;
+        const int b_second = (EPI == EPI_SWIGLU) ? b_first + p.N : b_first + 128;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (it >= STAGES && !mbar_wait(&empty_bar[s], ph ^ 1, p.status, abort)) break;
           unsigned char* st = smem + s * STAGE_BYTES;
-          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          tma_load_2d(st, &map_a, kb * BK, tl.row0, &full_bar[s]);
-          tma_load_2d(st + A_BYTES, &map_b, kb * BK, b_row0, &full_bar[s]);
-          tma_load_2d(st + A_BYTES + B_HALF_BYTES, &map_b, kb * BK, b_row1, &full_bar[s]);
+          if (CG == 1) {
+            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            tma_load_2d(st, &map_a, kb * BK, tl.row0, &full_bar[s]);
+            tma_load_2d(st + A_BYTES, &map_b, kb * BK, b_first, &full_bar[s]);
+            tma_load_2d(st + A_BYTES + B_HALF_BYTES, &map_b, kb * BK, b_second, &full_bar[s]);
+          } else {
+            // both CTAs' bytes are counted on the leader's barrier; only the leader announces them
+            if (leader) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+            tma_load_2d_pair(st, &map_a, kb * BK, tl.row0, &full_bar[s]);
+            tma_load_2d_pair(st + A_BYTES, &map_b, kb * BK, leader ? b_first : b_second, &full_bar[s]);
+          }
         }
       }
       if (*abort) {
-        // let my own loads that are still in flight land before the CTA's shared memory goes away
-        int quiet = 0;
+        // let the loads that are still in flight land before the CTA's shared memory goes away
+        // (a pair's follower cannot observe its own loads: they complete on the leader's barrier)
+        if (CG == 1 || leader) {
+          int quiet = 0;
+          for (uint32_t n = it > STAGES ? it - STAGES : 0; n < it; ++n)
+            mbar_wait(&full_bar[n % STAGES], (n / STAGES) & 1, nullptr, &quiet);
+        }
+      } else if (CG == 2) {
+        // a pair's CTA must not leave while the leader's last commits can still arrive on its barriers
         for (uint32_t n = it > STAGES ? it - STAGES : 0; n < it; ++n)
-          mbar_wait(&full_bar[n % STAGES], (n / STAGES) & 1, nullptr, &quiet);
+          if (!mbar_wait(&empty_bar[n % STAGES], (n / STAGES) & 1, p.status, abort)) break;
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (elect_one()) {
-      const uint32_t idesc = instr_desc_bf16(BM, BN);
+    // ---------------- MMA issuer (the leader CTA of a pair) ----------------
+    if (leader && elect_one()) {
+      const uint32_t idesc = instr_desc_bf16(TM, BN);
       uint32_t it = 0, tile_n = 0;
       Tile tl;
-      for (int t = blockIdx.x; decode_tile(t, s_tile_off, s_row_off, p.El, p.n_tiles, tl) && !*abort; t += gridDim.x, ++tile_n) {
+      for (int t = unit; decode_tile<TM>(t, s_tile_off, s_row_off, p.El, p.n_tiles, gm, cta_rank, tl) && !*abort; t += n_units, ++tile_n) {
         const int buf = tile_n & 1;
         const uint32_t use = tile_n >> 1;
         if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1, p.status, abort)) break;
@@ -146,12 +195,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
           const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)   // 16 bf16 = 32 bytes per MMA step: +2 in 16-byte units
-            mma_bf16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) ? 1u : 0u);
-          mma_commit(&empty_bar[s]);          // frees the smem stage when these MMAs retire
+          for (int k = 0; k < BK / 16; ++k) {  // 16 bf16 = 32 bytes per MMA step: +2 in 16-byte units
+            if (CG == 1) mma_bf16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+            else mma_bf16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+          }
+          // frees the smem stage (in both CTAs of a pair) when these MMAs retire
+          if (CG == 1) mma_commit(&empty_bar[s]); else mma_commit_pair(&empty_bar[s]);
         }
         if (!ok) break;
-        mma_commit(&acc_full[buf]);           // accumulator complete
+        // accumulator complete (announced to both epilogues of a pair)
+        if (CG == 1) mma_commit(&acc_full[buf]); else mma_commit_pair(&acc_full[buf]);
       }
     }
   } else {
@@ -160,7 +213,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     unsigned char* my_smem = epi_smem + (warp - 2) * EPI_WARP_BYTES;
     uint32_t tile_n = 0;
     Tile tl;
-    for (int t = blockIdx.x; decode_tile(t, s_tile_off, s_row_off, p.El, p.n_tiles, tl) && !*abort; t += gridDim.x, ++tile_n) {
+    for (int t = unit; decode_tile<TM>(t, s_tile_off, s_row_off, p.El, p.n_tiles, gm, cta_rank, tl) && !*abort; t += n_units, ++tile_n) {
       const int buf = tile_n & 1;
       if (!mbar_wait(&acc_full[buf], (tile_n >> 1) & 1, p.status, abort)) break;
       fence_after_sync();
@@ -171,7 +224,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (EPI == EPI_SWIGLU && row_ok && p.row_prob) prob = p.row_prob[my_row];
       constexpr int OUT_COLS = (EPI == EPI_SWIGLU) ? 128 : BN;
       const int col_base = tl.nt * OUT_COLS;
-      for (int c = 0; c < OUT_COLS / 64; ++c) {
+      for (int c = 0; c < OUT_COLS / 64 && tl.valid_rows > 0; ++c) {
         // ---- 64 output columns of my row -> registers -> bf16 -> my row of the staging tile
         uint32_t packed[32];
 #pragma unroll
@@ -229,16 +282,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (lane == 0) {
+        if (CG == 1) mbar_arrive(&acc_empty[buf]); else mbar_arrive_cluster(&acc_empty[buf], 0);
+      }
     }
   }
 
   // ---------------- teardown: every path arrives here ----------------
   fence_before_sync();
   __syncthreads();
+  __syncwarp();
+  if (CG == 2) cluster_sync_all();      // both epilogues are done with TMEM, nobody addresses the peer any more
   if (warp == 1) {
     fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
+    if (CG == 2) tmem_dealloc_pair(tmem_base, 512); else tmem_dealloc(tmem_base, 512);
   }
   if (EPI == EPI_COMBINE && p.signal_flag_off >= 0) {
     // all CTAs' peer stores done -> the last CTA raises this rank's combine flag on every peer
@@ -282,8 +339,63 @@ static int make_map(CUtensorMap* m, const void* base, long long rows, long long 
   return r == CUDA_SUCCESS ? 0 : 2;
 }
 
+// Number of CTA pairs that can be resident at once (the SMs of a pair share a GPC, so this can be
+// below SMs / 2); cached per epilogue. 0 if the query fails.
+template <int EPI>
+static int max_resident_pairs() {
+  static int cached = -1;
+  if (cached < 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, grouped_gemm_kernel<EPI, 2>, &cfg) != cudaSuccess) n = 0;
+    cached = n;
+  }
+  return cached;
+}
+
+template <int EPI>
+static int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, const PeerPtrs& peers,
+                      int ctas, bool pair, cudaStream_t st) {
+  if (!pair) {
+    if (cudaFuncSetAttribute(grouped_gemm_kernel<EPI, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return 4;
+    grouped_gemm_kernel<EPI, 1><<<ctas, GEMM_THREADS, SMEM_BYTES, st>>>(ma, mb, p, peers);
+    return 0;
+  }
+  if (cudaFuncSetAttribute(grouped_gemm_kernel<EPI, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    return 4;
+  int pairs = ctas / 2;
+  const int resident = max_resident_pairs<EPI>();
+  if (resident < 1) return 5;
+  if (pairs > resident) pairs = resident;
+  if (pairs < 1) pairs = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<EPI, 2>, ma, mb, p, peers) == cudaSuccess ? 0 : 5;
+}
+
 int launch_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, GemmParams p,
-                        const PeerPtrs& peers, int ctas, cudaStream_t st) {
+                        const PeerPtrs& peers, int ctas, bool pair, cudaStream_t st) {
   if (p.El < 1 || p.El > kMaxLocalExperts || p.K <= 0 || p.K % 8 || p.N <= 0 || p.N_out % 8) return 1;
   if (reinterpret_cast<uintptr_t>(a) % 16 || reinterpret_cast<uintptr_t>(w) % 16) return 1;
   if (epi == EPI_SWIGLU && (p.N % 128)) return 1;
@@ -292,17 +404,12 @@ int launch_grouped_gemm(const void* a, long long a_rows, const void* w, int epi,
   if (make_map(&mb, w, (long long)p.El * p.w_rows, p.K)) return 3;
   p.n_tiles = epi == EPI_SWIGLU ? p.N / 128 : (p.N + BN - 1) / BN;
   p.max_rows = (int)a_rows;
+  if (p.band_rows <= 0) p.band_rows = 2048;
   if (ctas < 1) ctas = 1;
-  cudaError_t e;
-#define B200EP_GEMM_LAUNCH(EPI)                                                                          \
-  e = cudaFuncSetAttribute(grouped_gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); \
-  if (e != cudaSuccess) return 4;                                                                        \
-  grouped_gemm_kernel<EPI><<<ctas, GEMM_THREADS, SMEM_BYTES, st>>>(ma, mb, p, peers)
-  if (epi == EPI_PLAIN) { B200EP_GEMM_LAUNCH(EPI_PLAIN); }
-  else if (epi == EPI_SWIGLU) { B200EP_GEMM_LAUNCH(EPI_SWIGLU); }
-  else if (epi == EPI_COMBINE) { B200EP_GEMM_LAUNCH(EPI_COMBINE); }
-  else return 1;
-  return 0;
+  if (epi == EPI_PLAIN) return launch_one<EPI_PLAIN>(ma, mb, p, peers, ctas, pair, st);
+  if (epi == EPI_SWIGLU) return launch_one<EPI_SWIGLU>(ma, mb, p, peers, ctas, pair, st);
+  if (epi == EPI_COMBINE) return launch_one<EPI_COMBINE>(ma, mb, p, peers, ctas, pair, st);
+  return 1;
 }
 
 }  // namespace b200ep

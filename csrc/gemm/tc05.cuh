@@ -1,7 +1,9 @@
 // Thin inline-PTX layer over the Blackwell tensor-core path used by the grouped GEMMs:
-// mbarriers with bounded waits, TMA tile loads of LOCAL memory (no cluster qualifier on any
-// load), tcgen05 shared-memory / instruction descriptors, MMA issue, commit, and TMEM
-// allocation / loads. sm_100a only.
+// mbarriers with bounded waits, TMA tile loads of LOCAL memory (every CTA fetches its own
+// tiles; no load is replicated to other CTAs), tcgen05 shared-memory / instruction
+// descriptors, MMA issue, commit, and TMEM allocation / loads, each in a one-CTA form and in
+// the CTA-pair form (`cta_group::2`: two CTAs of a cluster work on one 256-row tile, each
+// holding half of the weight tile). sm_100a only.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -65,6 +67,35 @@ __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
+// ---- CTA pair (cluster of two) -------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory object in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+// all threads of both CTAs; also orders mbarrier initialisation before the peer's first use
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on an mbarrier that lives in CTA `rank` of the cluster (own rank allowed)
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t rank) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_map(smem_u32(bar), rank)) : "memory");
+}
+// Pair form of the tile load: the data lands in THIS CTA's shared memory, the bytes are
+// counted on the mbarrier of the pair's leader (CTA rank 0), which alone waits for both halves.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(cluster_map(smem_u32(bar), 0)) : "memory");
+}
+
 // ---- tcgen05 descriptors ------------------------------------------------------------------
 // K-major operand tile in shared memory, 128-byte swizzle, rows of 128 bytes (64 bf16),
 // 8-row groups 1024 bytes apart. Tile base must be 1024-byte aligned.
@@ -91,6 +122,20 @@ __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t a_desc, uint6
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Pair forms, issued by one thread of the leader CTA: the MMA reads A (128 rows) and half of B
+// from each CTA's shared memory at the same offsets and writes 128 accumulator lanes in each
+// CTA's TMEM; the commit arrives on the barrier at the same offset in BOTH CTAs.
+__device__ __forceinline__ void mma_bf16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {
+  const unsigned short both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(both) : "memory");
+}
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -101,6 +146,14 @@ __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {       // whole warp
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Pair forms: the same warp of BOTH CTAs executes them.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets row (lane base + i).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {

@@ -12,7 +12,7 @@ with a steady clock around submit + stream synchronise; the slowest rank defines
 The best variant per (pattern, size) is written as a selector table that `ops/variants.py` loads.
 
     torchrun --nproc-per-node 8 -m gpu_data_transfer_profile_b200.bench.copy_sweep \
-        --min-bytes 4K --max-bytes 1G --jsonl gpurun_out/copy_sweep.jsonl --table gpurun_out/variant_table.json
+        --min-bytes 4K --max-bytes 1G --jsonl copy_sweep.jsonl --table variant_table.json
 """
 from __future__ import annotations
 

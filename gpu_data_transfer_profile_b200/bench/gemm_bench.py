@@ -1,6 +1,9 @@
 """Grouped expert GEMM throughput: this library's tcgen05 kernels vs the per-expert library
 GEMM loop (the reference's torch fallback, `DeepEP_Megatron/test_deepep_moe_dispatch_combine.py:590-600`).
 
+All variants are timed round-robin inside one loop (variant 1, variant 2, ..., variant 1, ...), so
+they see the same clocks and temperature; the figure of a variant is the median over its samples.
+
     python -m gpu_data_transfer_profile_b200.bench.gemm_bench --rows 16384 --hidden 4096 --ffn 14336 --experts 1
 """
 from __future__ import annotations
@@ -15,21 +18,27 @@ from ..ops import gemm as G
 from ..utils.timing import L2Flusher
 
 
-def _time(fn, iters, warmup, flush):
+def _time_round_robin(fns, iters, warmup, flush):
+    """fns: {name: callable}. Returns {name: (median ms, best ms)}."""
     for _ in range(warmup):
-        fn()
+        for fn in fns.values():
+            fn()
     torch.cuda.synchronize()
-    ms = []
+    ms = {k: [] for k in fns}
     for _ in range(iters):
-        flush()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn()
-        b.record()
-        b.synchronize()
-        ms.append(a.elapsed_time(b))
-    ms.sort()
-    return ms[len(ms) // 2], ms[0]
+        for name, fn in fns.items():
+            flush()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            ms[name].append(a.elapsed_time(b))
+    out = {}
+    for k, v in ms.items():
+        v.sort()
+        out[k] = (v[len(v) // 2], v[0])
+    return out
 
 
 def main() -> int:
@@ -41,6 +50,10 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--skip-torch", action="store_true")
+    ap.add_argument("--form", choices=["cta", "pair", "both"], default="both",
+                    help="cta: one CTA per 128x256 tile; pair: a CTA pair (cta_group::2) per 256x256 tile")
+    ap.add_argument("--band-mb", type=str, default="",
+                    help="comma-separated L2 band sizes (MiB) of the tile order to compare; empty = the default")
     args = ap.parse_args()
     dev = torch.device("cuda")
     E, H, F, rows = args.experts, args.hidden, args.ffn, args.rows
@@ -59,13 +72,19 @@ def main() -> int:
     if os.path.exists(p):
         peaks = json.load(open(p))
     peak = peaks.get("bf16_tflops", 1590.0)
-    res = {}
     f1 = 2.0 * rows * H * 2 * F
     f2 = 2.0 * rows * F * H
-    med, best = _time(lambda: G.grouped_gemm_swiglu(x, w1, off, prob, out=act), args.iters, args.warmup, flush)
-    res["fc1_swiglu_tcgen05"] = dict(ms=med, best_ms=best, tflops=f1 / med / 1e9, frac_of_measured_peak=f1 / med / 1e9 / peak)
-    med, best = _time(lambda: G.grouped_gemm(act, w2, off, out=out), args.iters, args.warmup, flush)
-    res["fc2_tcgen05"] = dict(ms=med, best_ms=best, tflops=f2 / med / 1e9, frac_of_measured_peak=f2 / med / 1e9 / peak)
+    bands = [int(float(b) * (1 << 20)) for b in args.band_mb.split(",") if b] or [None]
+    fns, flops = {}, {}
+    for form in (["cta", "pair"] if args.form == "both" else [args.form]):
+        pair = form == "pair"
+        for band in bands:
+            tag = ("_pair" if pair else "") + (f"_band{band >> 20}" if band else "")
+            fns["fc1_swiglu_tcgen05" + tag] = (
+                lambda pair=pair, band=band: G.grouped_gemm_swiglu(x, w1, off, prob, out=act, pair=pair, band_bytes=band))
+            fns["fc2_tcgen05" + tag] = (
+                lambda pair=pair, band=band: G.grouped_gemm(act, w2, off, out=out, pair=pair, band_bytes=band))
+            flops["fc1_swiglu_tcgen05" + tag], flops["fc2_tcgen05" + tag] = f1, f2
     if not args.skip_torch:
         def torch_fc1():
             r = 0
@@ -80,10 +99,13 @@ def main() -> int:
             for e, c in enumerate(counts):
                 out[r:r + c] = torch.nn.functional.linear(act[r:r + c], w2[e])
                 r += c
-        med, best = _time(torch_fc1, args.iters, args.warmup, flush)
-        res["fc1_swiglu_torch"] = dict(ms=med, best_ms=best, tflops=f1 / med / 1e9)
-        med, best = _time(torch_fc2, args.iters, args.warmup, flush)
-        res["fc2_torch"] = dict(ms=med, best_ms=best, tflops=f2 / med / 1e9)
+        fns["fc1_swiglu_torch"], fns["fc2_torch"] = torch_fc1, torch_fc2
+        flops["fc1_swiglu_torch"], flops["fc2_torch"] = f1, f2
+    res = {}
+    for name, (med, best) in _time_round_robin(fns, args.iters, args.warmup, flush).items():
+        res[name] = dict(ms=med, best_ms=best, tflops=flops[name] / med / 1e9)
+        if "torch" not in name:
+            res[name]["frac_of_measured_peak"] = flops[name] / med / 1e9 / peak
     print(json.dumps(dict(bench="gemm", rows=rows, hidden=H, ffn=F, experts=E, peak_tflops_measured=peak, **res)))
     return 0
 

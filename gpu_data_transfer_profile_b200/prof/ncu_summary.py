@@ -2,7 +2,7 @@
 profiles/: duration, DRAM bytes and throughput, tensor-pipe activity, warps, registers, and the
 achieved fraction of the measured roofline.
 
-    ncu -i gpurun_out/prof.ncu-rep --page raw --csv > raw.csv
+    ncu -i prof.ncu-rep --page raw --csv > raw.csv
     python -m gpu_data_transfer_profile_b200.prof.ncu_summary raw.csv --kernel grouped_gemm --flops 2.4e12
 """
 from __future__ import annotations

@@ -30,7 +30,7 @@ def _worker(rank, world, port, q):
     d = AllToAllTokenDispatcher(dist.group.WORLD, 4)
     d.dispatch(x, idx, w)                      # one healthy round
     if rank == 1:
-        _say(q, (rank, "left"))                # this rank "fails" between steps: it never joins round 2
+        _say(q, (rank, "left"))                # this rank "fails" between steps: it never joins the second collective
         os._exit(0)
     try:
         d.dispatch(x, idx, w)
