@@ -12,7 +12,8 @@ struct GemmParams {
   int N;                  // plain/combine: output features; swiglu: F (gate and linear blocks of F rows each)
   int K;                  // reduction length
   int N_out;              // columns of the stored result (== N)
-  int w_rows;             // rows per expert in the weight tensor (N, or 2F for swiglu)
+  int w_rows;             // rows per expert in the weight tensor (N, or 2F for swiglu; K if b_mn)
+  int b_mn;               // 1: weights stored [El, K, N] (N contiguous), plain epilogue only
   int n_tiles, max_rows;  // filled by the launcher
   int band_rows;          // activation rows per L2-resident band of the tile order (<= 0: 2048)
   const int* expert_off;  // device [El+1]: exclusive prefix of rows per local expert
@@ -33,6 +34,20 @@ struct GemmParams {
 // CTAs on 128 x 256 tiles; `ctas` then counts CTAs as well (pairs = ctas / 2, capped by residency).
 int launch_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, GemmParams p,
                         const PeerPtrs& peers, int ctas, bool pair, cudaStream_t st);
+
+// Weight gradient of a grouped GEMM: dW[e] = G_e^T . X_e over the rows of local expert e.
+struct WgradParams {
+  int El;                 // local experts
+  int M, N;               // dW[e] is [M, N]: M = columns of G, N = columns of X
+  int max_rows;           // filled by the launcher
+  const int* expert_off;  // device [El+1]
+  void* out;              // bf16 [El, M, N]
+  int* status;
+};
+// g: bf16 [rows, M], x: bf16 [rows, N], both on this GPU, rows grouped by local expert.
+// pair: CTA pairs on 256 x 256 tiles of dW (M % 256 == 0) instead of single CTAs on 128 x 256 (M % 128 == 0).
+int launch_grouped_wgrad(const void* g, const void* x, long long rows, WgradParams p, int ctas, bool pair,
+                         cudaStream_t st);
 
 // SwiGLU x prob elementwise pair for the training path (h: bf16 [rows, 2F], gate columns first).
 // n_rows_ptr (device, optional) bounds the rows actually processed; max_rows is the tensor's size.

@@ -26,6 +26,7 @@
 // Every mbarrier wait is bounded; on a time-out all roles leave their loops, TMEM is freed.
 #include <cuda_bf16.h>
 #include "tc05.cuh"
+#include "tmap.h"
 #include "gemm_api.h"
 
 namespace b200ep {
@@ -78,7 +79,10 @@ __device__ __forceinline__ bool decode_tile(int t, const int* s_tile_off, const 
 
 __device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
 
-template <int EPI, int CG>
+// BMN: the weights are stored [E_local, K, N] (N contiguous) instead of [E_local, N, K]; they are
+// then read as an N-major operand (64 x 64 boxes, one 128-byte row of 64 outputs per reduction
+// index), which is how the data gradients use the forward weights without a transposed copy.
+template <int EPI, int CG, bool BMN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ GemmParams p, const __grid_constant__ PeerPtrs peers) {
@@ -147,7 +151,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const uint32_t ph = (it / STAGES) & 1;
           if (it >= STAGES && !mbar_wait(&empty_bar[s], ph ^ 1, p.status, abort)) break;
           unsigned char* st = smem + s * STAGE_BYTES;
-          if (CG == 1) {
+          if (BMN) {
+            // weights [K, N] per expert: boxes of 64 reduction rows x 64 output columns. A reduction
+            // tail that runs into the next expert's rows meets zero-filled columns of A.
+            constexpr int NBOX = CG == 1 ? 4 : 2;
+            const int n0 = tl.nt * BN + (CG == 2 ? cta_rank * 128 : 0);
+            const int krow = tl.e * p.w_rows + kb * BK;
+            if (CG == 1) {
+              mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+              tma_load_2d(st, &map_a, kb * BK, tl.row0, &full_bar[s]);
+#pragma unroll
+              for (int b = 0; b < NBOX; ++b) tma_load_2d(st + A_BYTES + b * 8192, &map_b, n0 + b * 64, krow, &full_bar[s]);
+            } else {
+              if (leader) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+              tma_load_2d_pair(st, &map_a, kb * BK, tl.row0, &full_bar[s]);
+#pragma unroll
+              for (int b = 0; b < NBOX; ++b) tma_load_2d_pair(st + A_BYTES + b * 8192, &map_b, n0 + b * 64, krow, &full_bar[s]);
+            }
+          } else if (CG == 1) {
             mbar_expect_tx(&full_bar[s], STAGE_BYTES);
             tma_load_2d(st, &map_a, kb * BK, tl.row0, &full_bar[s]);
             tma_load_2d(st + A_BYTES, &map_b, kb * BK, b_first, &full_bar[s]);
@@ -177,7 +198,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else if (warp == 1) {
     // ---------------- MMA issuer (the leader CTA of a pair) ----------------
     if (leader && elect_one()) {
-      const uint32_t idesc = instr_desc_bf16(TM, BN);
+      const uint32_t idesc = instr_desc_bf16(TM, BN, false, BMN);
       uint32_t it = 0, tile_n = 0;
       Tile tl;
       for (int t = unit; decode_tile<TM>(t, s_tile_off, s_row_off, p.El, p.n_tiles, gm, cta_rank, tl) && !*abort; t += n_units, ++tile_n) {
@@ -193,11 +214,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (!mbar_wait(&full_bar[s], ph, p.status, abort)) { ok = false; break; }
           fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-          const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(a_addr + A_BYTES);
+          const uint64_t a_desc = smem_desc_sw128(a_addr);
+          const uint64_t b_desc = BMN ? smem_desc_mn_sw128(a_addr + A_BYTES, 8192) : smem_desc_sw128(a_addr + A_BYTES);
+          // per MMA step of 16 reduction indices: K-major +32 bytes (2 units), N-major +16 rows of 128 bytes (128 units)
+          constexpr int B_STEP = BMN ? 128 : 2;
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {  // 16 bf16 = 32 bytes per MMA step: +2 in 16-byte units
-            if (CG == 1) mma_bf16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) ? 1u : 0u);
-            else mma_bf16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+          for (int k = 0; k < BK / 16; ++k) {
+            if (CG == 1) mma_bf16(d_tmem, a_desc + 2 * k, b_desc + B_STEP * k, idesc, (kb | k) ? 1u : 0u);
+            else mma_bf16_pair(d_tmem, a_desc + 2 * k, b_desc + B_STEP * k, idesc, (kb | k) ? 1u : 0u);
           }
           // frees the smem stage (in both CTAs of a pair) when these MMAs retire
           if (CG == 1) mma_commit(&empty_bar[s]); else mma_commit_pair(&empty_bar[s]);
@@ -309,39 +333,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---- host side -----------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  return fn;
-}
-
-// 2-D bf16 tensor [rows, cols] (cols contiguous), box = 64 cols x 128 rows, 128-byte swizzle.
+// operand maps: box = 64 columns (one 128-byte swizzle row) x 128 rows
 static int make_map(CUtensorMap* m, const void* base, long long rows, long long cols) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return 1;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {BK, 128};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : 2;
+  return make_tmap_bf16(m, base, rows, cols, BK, 128);
 }
 
 // Number of CTA pairs that can be resident at once (the SMs of a pair share a GPC, so this can be
 // below SMs / 2); cached per epilogue. 0 if the query fails.
-template <int EPI>
+template <int EPI, bool BMN>
 static int max_resident_pairs() {
   static int cached = -1;
   if (cached < 0) {
@@ -357,25 +356,25 @@ static int max_resident_pairs() {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, grouped_gemm_kernel<EPI, 2>, &cfg) != cudaSuccess) n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, grouped_gemm_kernel<EPI, 2, BMN>, &cfg) != cudaSuccess) n = 0;
     cached = n;
   }
   return cached;
 }
 
-template <int EPI>
+template <int EPI, bool BMN>
 static int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, const PeerPtrs& peers,
                       int ctas, bool pair, cudaStream_t st) {
   if (!pair) {
-    if (cudaFuncSetAttribute(grouped_gemm_kernel<EPI, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(grouped_gemm_kernel<EPI, 1, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return 4;
-    grouped_gemm_kernel<EPI, 1><<<ctas, GEMM_THREADS, SMEM_BYTES, st>>>(ma, mb, p, peers);
+    grouped_gemm_kernel<EPI, 1, BMN><<<ctas, GEMM_THREADS, SMEM_BYTES, st>>>(ma, mb, p, peers);
     return 0;
   }
-  if (cudaFuncSetAttribute(grouped_gemm_kernel<EPI, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+  if (cudaFuncSetAttribute(grouped_gemm_kernel<EPI, 2, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
     return 4;
   int pairs = ctas / 2;
-  const int resident = max_resident_pairs<EPI>();
+  const int resident = max_resident_pairs<EPI, BMN>();
   if (resident < 1) return 5;
   if (pairs > resident) pairs = resident;
   if (pairs < 1) pairs = 1;
@@ -391,7 +390,7 @@ static int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<EPI, 2>, ma, mb, p, peers) == cudaSuccess ? 0 : 5;
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<EPI, 2, BMN>, ma, mb, p, peers) == cudaSuccess ? 0 : 5;
 }
 
 int launch_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, GemmParams p,
@@ -401,14 +400,18 @@ int launch_grouped_gemm(const void* a, long long a_rows, const void* w, int epi,
   if (epi == EPI_SWIGLU && (p.N % 128)) return 1;
   CUtensorMap ma, mb;
   if (make_map(&ma, a, a_rows, p.K)) return 3;
-  if (make_map(&mb, w, (long long)p.El * p.w_rows, p.K)) return 3;
+  if (p.b_mn) {
+    if (epi != EPI_PLAIN) return 1;
+    if (make_tmap_bf16(&mb, w, (long long)p.El * p.w_rows, p.N, 64, BK)) return 3;
+  } else if (make_map(&mb, w, (long long)p.El * p.w_rows, p.K)) return 3;
   p.n_tiles = epi == EPI_SWIGLU ? p.N / 128 : (p.N + BN - 1) / BN;
   p.max_rows = (int)a_rows;
   if (p.band_rows <= 0) p.band_rows = 2048;
   if (ctas < 1) ctas = 1;
-  if (epi == EPI_PLAIN) return launch_one<EPI_PLAIN>(ma, mb, p, peers, ctas, pair, st);
-  if (epi == EPI_SWIGLU) return launch_one<EPI_SWIGLU>(ma, mb, p, peers, ctas, pair, st);
-  if (epi == EPI_COMBINE) return launch_one<EPI_COMBINE>(ma, mb, p, peers, ctas, pair, st);
+  if (epi == EPI_PLAIN && p.b_mn) return launch_one<EPI_PLAIN, true>(ma, mb, p, peers, ctas, pair, st);
+  if (epi == EPI_PLAIN) return launch_one<EPI_PLAIN, false>(ma, mb, p, peers, ctas, pair, st);
+  if (epi == EPI_SWIGLU) return launch_one<EPI_SWIGLU, false>(ma, mb, p, peers, ctas, pair, st);
+  if (epi == EPI_COMBINE) return launch_one<EPI_COMBINE, false>(ma, mb, p, peers, ctas, pair, st);
   return 1;
 }
 

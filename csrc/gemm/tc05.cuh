@@ -108,9 +108,28 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                        // layout: 128-byte swizzle
   return d;
 }
-// bf16 x bf16 -> f32, both operands K-major, tile M x N.
-__device__ __forceinline__ uint32_t instr_desc_bf16(int M, int N) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+// M/N-major operand tile (the M or N index is contiguous in memory, the reduction index is the
+// row): rows of 128 bytes = 64 bf16 along M/N, one row per reduction index, 128-byte swizzle,
+// 8-row groups 1024 bytes apart; the next 64 elements along M/N start `mn_group_bytes` further
+// (a tile wider than 64 elements is stored as several such column blocks). 1024-byte aligned base.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_group_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
+  d |= (uint64_t)((mn_group_bytes >> 4) & 0x3fff) << 16;   // leading byte offset: between 64-element M/N blocks
+  d |= (uint64_t)(1024 >> 4) << 32;                         // stride byte offset: between 8-row groups
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// bf16 x bf16 -> f32, tile M x N; a_mn / b_mn: that operand is M/N-major instead of K-major.
+__device__ __forceinline__ uint32_t instr_desc_bf16(int M, int N, bool a_mn = false, bool b_mn = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// Makes this thread's ordinary shared-memory writes visible to the tensor core / TMA path
+// (needed when threads patch an operand tile that an MMA will read).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(

@@ -50,6 +50,7 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--skip-torch", action="store_true")
+    ap.add_argument("--wgrad", action="store_true", help="also time the two weight-gradient GEMMs (ragged reduction)")
     ap.add_argument("--form", choices=["cta", "pair", "both"], default="both",
                     help="cta: one CTA per 128x256 tile; pair: a CTA pair (cta_group::2) per 256x256 tile")
     ap.add_argument("--band-mb", type=str, default="",
@@ -85,6 +86,25 @@ def main() -> int:
             fns["fc2_tcgen05" + tag] = (
                 lambda pair=pair, band=band: G.grouped_gemm(act, w2, off, out=out, pair=pair, band_bytes=band))
             flops["fc1_swiglu_tcgen05" + tag], flops["fc2_tcgen05" + tag] = f1, f2
+    if args.wgrad:
+        dh = torch.randn(rows, 2 * F, device=dev).to(torch.bfloat16)
+        dy = torch.randn(rows, H, device=dev).to(torch.bfloat16)
+        dw1, dw2 = torch.empty_like(w1), torch.empty_like(w2)
+        for form in (["cta", "pair"] if args.form == "both" else [args.form]):
+            pair = form == "pair"
+            tag = "_pair" if pair else ""
+            fns["wgrad1_tcgen05" + tag] = lambda pair=pair: G.grouped_wgrad(dh, x, off, out=dw1, pair=pair)
+            fns["wgrad2_tcgen05" + tag] = lambda pair=pair: G.grouped_wgrad(dy, act, off, out=dw2, pair=pair)
+            flops["wgrad1_tcgen05" + tag], flops["wgrad2_tcgen05" + tag] = f1, f2
+        if not args.skip_torch:
+            def torch_wgrad(gg, xx, dw):
+                r = 0
+                for e, c in enumerate(counts):
+                    torch.mm(gg[r:r + c].t(), xx[r:r + c], out=dw[e])
+                    r += c
+            fns["wgrad1_torch"] = lambda: torch_wgrad(dh, x, dw1)
+            fns["wgrad2_torch"] = lambda: torch_wgrad(dy, act, dw2)
+            flops["wgrad1_torch"], flops["wgrad2_torch"] = f1, f2
     if not args.skip_torch:
         def torch_fc1():
             r = 0

@@ -2,8 +2,11 @@
 
 Forward: fc1 with SwiGLU x probability fused into its epilogue (one kernel), fc2 either as a
 plain grouped GEMM or with the combine send fused into its epilogue (`forward_fused_combine`).
-Tile scheduling reads the per-expert row offsets on the device. Backward runs the same math with
-library GEMMs through PyTorch (dgrad/wgrad kernels of this library are future work).
+Tile scheduling reads the per-expert row offsets on the device. Backward (SwiGLU path): the two
+data gradients run on the same grouped GEMM reading the forward weights in place as an N-major
+operand, the two weight gradients on the ragged-reduction kernel (`ops.gemm.grouped_wgrad`), the
+element-wise part on the fused SwiGLU backward kernel; no library GEMM and no host-side split.
+Other activations fall back to autograd over per-expert library GEMMs.
 """
 from __future__ import annotations
 
@@ -36,8 +39,11 @@ def _mlp_backward(x, w1, w2, probs, counts, dy, gated, activation):
     return dx, dw1, dw2, dp
 
 
-def _wgrad(dy, a, counts, out_shape):
-    """dW[e] = dy_e^T @ a_e per local expert (library GEMM; split sizes are host-known here)."""
+def _wgrad(dy, a, counts, out_shape, expert_off=None):
+    """dW[e] = dy_e^T @ a_e per local expert: the tcgen05 ragged-reduction kernel when the shapes
+    allow it (dW rows a multiple of 128), else a library GEMM per expert."""
+    if expert_off is not None and out_shape[1] % 128 == 0 and out_shape[2] % 8 == 0 and dy.shape[0] > 0:
+        return G.grouped_wgrad(dy.contiguous(), a.contiguous(), expert_off)
     dw = torch.zeros(out_shape, dtype=dy.dtype, device=dy.device)
     r = 0
     for e, c in enumerate(counts):
@@ -50,7 +56,8 @@ def _wgrad(dy, a, counts, out_shape):
 class _GroupedMLP(torch.autograd.Function):
     """Training path. SwiGLU: fc1 (tcgen05, plain epilogue, keeps the pre-activation h) -> fused
     swiglu x prob kernel -> fc2 (tcgen05). Backward: fused swiglu backward kernel, both dgrads on
-    the tcgen05 grouped GEMM with transposed weights, wgrads with the library GEMM."""
+    the tcgen05 grouped GEMM (weights read in place, N-major), both wgrads on the tcgen05
+    ragged-reduction kernel."""
 
     @staticmethod
     def forward(ctx, x, w1, w2, probs, expert_off, counts, activation):
@@ -76,11 +83,11 @@ class _GroupedMLP(torch.autograd.Function):
             return dx, dw1, dw2, dp, None, None, None
         x, w1, w2, probs, h, act = ctx.saved_tensors
         rows = sum(ctx.counts)
-        dact = G.grouped_gemm(dy, w2.transpose(1, 2).contiguous(), ctx.off)          # [rows, F]
+        dact = G.grouped_gemm(dy, w2, ctx.off, w_kn=True)                             # [rows, F]
         dh, dp = G.swiglu_bwd(h, probs, dact)
-        dx = G.grouped_gemm(dh, w1.transpose(1, 2).contiguous(), ctx.off)            # [rows, H]
-        dw2 = _wgrad(dy[:rows], act[:rows], ctx.counts, w2.shape)
-        dw1 = _wgrad(dh[:rows], x[:rows], ctx.counts, w1.shape)
+        dx = G.grouped_gemm(dh, w1, ctx.off, w_kn=True)                               # [rows, H]
+        dw2 = _wgrad(dy[:rows], act[:rows], ctx.counts, w2.shape, ctx.off)
+        dw1 = _wgrad(dh[:rows], x[:rows], ctx.counts, w1.shape, ctx.off)
         return dx, dw1, dw2, dp, None, None, None
 
 
@@ -104,11 +111,11 @@ class _GroupedMLPFusedCombine(torch.autograd.Function):
         x, w1, w2, probs, h, act = ctx.saved_tensors
         dy, *_ = ctx.buffer.dispatch(grad_out.contiguous(), handle=ctx.handle)
         rows = sum(ctx.counts)
-        dact = G.grouped_gemm(dy, w2.transpose(1, 2).contiguous(), ctx.off)
+        dact = G.grouped_gemm(dy, w2, ctx.off, w_kn=True)
         dh, dp = G.swiglu_bwd(h, probs, dact)
-        dx = G.grouped_gemm(dh, w1.transpose(1, 2).contiguous(), ctx.off)
-        dw2 = _wgrad(dy[:rows], act[:rows], ctx.counts, w2.shape)
-        dw1 = _wgrad(dh[:rows], x[:rows], ctx.counts, w1.shape)
+        dx = G.grouped_gemm(dh, w1, ctx.off, w_kn=True)
+        dw2 = _wgrad(dy[:rows], act[:rows], ctx.counts, w2.shape, ctx.off)
+        dw1 = _wgrad(dh[:rows], x[:rows], ctx.counts, w1.shape, ctx.off)
         return dx, dw1, dw2, dp, None, None, None, None
 
 

@@ -46,12 +46,15 @@ def offsets_from_counts(tokens_per_expert, device) -> torch.Tensor:
 
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, expert_off: torch.Tensor, *, out: Optional[torch.Tensor] = None,
-                 ctas: int = 0, pair: Optional[bool] = None, band_bytes: Optional[int] = None) -> torch.Tensor:
-    """out[r] = a[r] @ w[e(r)].T   (a bf16 [rows,K], w bf16 [E,N,K]) -> bf16 [rows,N]"""
+                 ctas: int = 0, pair: Optional[bool] = None, band_bytes: Optional[int] = None,
+                 w_kn: bool = False) -> torch.Tensor:
+    """out[r] = a[r] @ w[e(r)].T   (a bf16 [rows,K], w bf16 [E,N,K]) -> bf16 [rows,N].
+    w_kn=True: w is stored [E,K,N] and out[r] = a[r] @ w[e(r)] (the data gradient of a layer whose
+    forward weight is [E,K,N]-shaped, read in place without a transposed copy)."""
     if out is None:
-        out = torch.empty((a.shape[0], w.shape[1]), dtype=torch.bfloat16, device=a.device)
+        out = torch.empty((a.shape[0], w.shape[2] if w_kn else w.shape[1]), dtype=torch.bfloat16, device=a.device)
     _ext.load().grouped_gemm(a, w, expert_off, PLAIN, out, None, None, [], 0, 0, 0, -1, 0, None, 0,
-                             ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes))
+                             ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes), w_kn)
     return out
 
 
@@ -63,7 +66,7 @@ def grouped_gemm_swiglu(a: torch.Tensor, w: torch.Tensor, expert_off: torch.Tens
     if out is None:
         out = torch.empty((a.shape[0], F), dtype=torch.bfloat16, device=a.device)
     _ext.load().grouped_gemm(a, w, expert_off, SWIGLU, out, row_prob, None, [], 0, 0, 0, -1, 0, None, 0,
-                             ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes))
+                             ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes), False)
     return out
 
 
@@ -74,7 +77,20 @@ def grouped_gemm_combine(a: torch.Tensor, w: torch.Tensor, expert_off: torch.Ten
     """fc2 with the combine send fused into the epilogue: row r of a @ w[e].T is stored into slot
     recv_meta[r,0] of rank recv_meta[r,1]'s combine region (peer LSU stores)."""
     _ext.load().grouped_gemm(a, w, expert_off, COMBINE, None, None, recv_meta, list(peers), comb_off, slot_cap,
-                             rank, signal_flag_off, epoch, counter, status_ptr, ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes))
+                             rank, signal_flag_off, epoch, counter, status_ptr, ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes), False)
+
+
+def grouped_wgrad(g: torch.Tensor, x: torch.Tensor, expert_off: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+                  ctas: int = 0, pair: Optional[bool] = None) -> torch.Tensor:
+    """dW[e] = g_e.T @ x_e over the rows of local expert e (g bf16 [rows,M], x bf16 [rows,N]) -> bf16 [E,M,N].
+    Both operands are read as stored; an expert without rows gets zeros. M % 128 == 0 (the pair form
+    needs M % 256 == 0 and is skipped otherwise), N % 8 == 0."""
+    E = expert_off.numel() - 1
+    if out is None:
+        out = torch.empty((E, g.shape[1], x.shape[1]), dtype=torch.bfloat16, device=g.device)
+    use_pair = _pair(pair) and g.shape[1] % 256 == 0
+    _ext.load().grouped_wgrad(g, x, expert_off, out, 0, ctas or _ctas(g.device), use_pair)
+    return out
 
 
 def swiglu_fwd(h: torch.Tensor, row_prob: Optional[torch.Tensor]) -> torch.Tensor:

@@ -34,6 +34,22 @@ def test_grouped_gemm_plain(counts, N, K, pair):
 
 
 @pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("counts,N,K", [([128], 256, 64), ([100, 0, 333, 7], 320, 256), ([513, 31], 384, 1000),
+                                        ([1000, 129, 2300], 768, 448)])
+def test_grouped_gemm_weights_stored_k_by_n(counts, N, K, pair):
+    """out[r] = a[r] @ w[e] with w stored [E, K, N]: the data-gradient form, weights read in place."""
+    from gpu_data_transfer_profile_b200.ops import gemm as G
+    torch.manual_seed(4)
+    rows = sum(counts)
+    a = torch.randn(rows, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(len(counts), K, N, device="cuda") * 0.1).to(torch.bfloat16)
+    out = G.grouped_gemm(a, w, G.offsets_from_counts(counts, "cuda"), pair=pair, w_kn=True)
+    torch.cuda.synchronize()
+    ref = _ref(a, w.transpose(1, 2), counts)
+    torch.testing.assert_close(out.float(), ref, atol=0.05 * (K ** 0.5) * 0.1, rtol=2e-2)
+
+
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("counts,F,K", [([128], 128, 128), ([200, 56], 256, 256), ([1, 300], 384, 192),
                                         ([700, 3, 257], 512, 512)])
 def test_grouped_gemm_swiglu_prob(counts, F, K, pair):
@@ -48,6 +64,29 @@ def test_grouped_gemm_swiglu_prob(counts, F, K, pair):
     fc1 = _ref(a, w, counts)
     ref = torch.nn.functional.silu(fc1[:, :F]) * fc1[:, F:] * prob[:, None]
     torch.testing.assert_close(out.float(), ref, atol=0.06, rtol=3e-2)
+
+
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("counts,M,N", [([64], 256, 256), ([128, 192], 256, 512), ([100, 0, 333, 7], 256, 320),
+                                        ([1], 512, 64), ([513, 63, 65], 768, 264), ([0, 0, 40], 256, 128),
+                                        ([1000, 129, 2300], 512, 1024)])
+def test_grouped_wgrad(counts, M, N, pair):
+    """dW[e] = g_e^T x_e with the reduction over each expert's (ragged) rows; rows after the last
+    expert hold NaN and must not leak into any gradient."""
+    from gpu_data_transfer_profile_b200.ops import gemm as G
+    torch.manual_seed(3)
+    rows = sum(counts)
+    g = torch.randn(rows + 70, M, device="cuda").to(torch.bfloat16)
+    x = torch.randn(rows + 70, N, device="cuda").to(torch.bfloat16)
+    g[rows:] = float("nan")
+    x[rows:] = float("nan")
+    dw = G.grouped_wgrad(g, x, G.offsets_from_counts(counts, "cuda"), pair=pair)
+    torch.cuda.synchronize()
+    r = 0
+    for e, c in enumerate(counts):
+        ref = g[r:r + c].float().t() @ x[r:r + c].float()
+        torch.testing.assert_close(dw[e].float(), ref, atol=0.05 * max(c, 1) ** 0.5, rtol=2e-2)
+        r += c
 
 
 def test_grouped_gemm_rejects_bad_shapes():
