@@ -141,3 +141,35 @@ def test_tcgen05_experts_backward_matches_torch_experts():
     torch.testing.assert_close(pa.grad, pb.grad, atol=0.5, rtol=5e-2)
     torch.testing.assert_close(a.weight1.grad.float(), b.weight1.grad, atol=0.15, rtol=5e-2)
     torch.testing.assert_close(a.weight2.grad.float(), b.weight2.grad, atol=0.15, rtol=5e-2)
+
+
+def test_tcgen05_expert_mlp_gradients_match_fp32_autograd():
+    """Training path of the expert MLP (tcgen05 forward, dgrads reading the weights in place,
+    ragged-reduction wgrads, fused SwiGLU backward) against fp32 autograd of the same math."""
+    from gpu_data_transfer_profile_b200.models.experts_tcgen05 import Tcgen05GroupedExperts
+    torch.manual_seed(5)
+    H, F, counts = 256, 384, [70, 0, 301, 129]
+    rows = sum(counts)
+    mod = Tcgen05GroupedExperts(len(counts), H, F, init_std=0.05)
+    x = torch.randn(rows, H, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    p = torch.rand(rows, device="cuda").requires_grad_(True)
+    gy = torch.randn(rows, H, device="cuda").to(torch.bfloat16)
+    y = mod(x, counts, p)
+    y.backward(gy)
+    xf = x.detach().float().requires_grad_(True)
+    pf = p.detach().clone().requires_grad_(True)
+    w1 = mod.weight1.detach().float().requires_grad_(True)
+    w2 = mod.weight2.detach().float().requires_grad_(True)
+    outs, r = [], 0
+    for e, c in enumerate(counts):
+        h = xf[r:r + c] @ w1[e].t()
+        a = torch.nn.functional.silu(h[:, :F]) * h[:, F:] * pf[r:r + c, None]
+        outs.append(a @ w2[e].t())
+        r += c
+    yr = torch.cat(outs)
+    yr.backward(gy.float())
+    torch.testing.assert_close(y.float(), yr.detach(), atol=3e-2, rtol=5e-2)
+    torch.testing.assert_close(x.grad.float(), xf.grad, atol=3e-2, rtol=5e-2)
+    torch.testing.assert_close(p.grad, pf.grad, atol=5e-2, rtol=5e-2)
+    torch.testing.assert_close(mod.weight1.grad.float(), w1.grad, atol=6e-2, rtol=5e-2)
+    torch.testing.assert_close(mod.weight2.grad.float(), w2.grad, atol=6e-2, rtol=5e-2)
