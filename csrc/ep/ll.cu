@@ -19,8 +19,9 @@ namespace b200ep {
 
 constexpr int kLLThreads = 256;  // 8 warps work on one row together
 
-// Per-op device state (4 ints): [0] committed epoch, [1] committed arrival target,
-// [2] epoch published by the send half, [3] target published by the send half.
+// Per-op device state (6 ints): [0] committed epoch, [1] committed arrival target,
+// [2] epoch published by the send half, [3] target published by the send half,
+// [4] cumulative count of send CTAs that have finished (signal mode 1), [5] unused.
 // Send half: works with epoch = [0]+1, target = [1]+grid; CTA 0 publishes them in [2],[3].
 // Receive half (next launch on the stream): reads [2],[3]; CTA 0 commits them to [0],[1].
 // No kernel ever reads a word that another CTA of the same launch writes.
@@ -46,15 +47,34 @@ __device__ __forceinline__ LLTick ll_tick_recv(int* st) {
   __syncthreads();
   return LLTick{s_e, s_t};
 }
-// Every CTA of a send kernel ends with this: its stores become visible system-wide, then it
-// adds 1 to this rank's arrival counter on every peer. A receiver waits for counter >= target,
-// i.e. for ALL CTAs of that sender (the grid size is the same on every rank), so no CTA has to
-// wait for the others and no second fence follows a "last block".
-__device__ __forceinline__ void ll_arrive_on_peers(const LLParams& P, const PeerPtrs& peers, int channel) {
+// Every CTA of a send kernel ends with this. A receiver waits for this rank's arrival counter
+// (one per peer and channel, cumulative) to reach the target, i.e. for ALL CTAs of the sender
+// (the grid size is the same on every rank). Two ways to get there (P.signal_mode):
+//  0: every CTA makes its stores visible system-wide and adds 1 to the counter on every peer:
+//     no CTA waits for the others, but a receiver takes R x grid remote atomics on R words;
+//  1: every CTA makes its stores visible and counts itself on a LOCAL cumulative counter
+//     (state[4]); the CTA that completes a multiple of the grid size adds the whole grid size to
+//     the counter on every peer: R remote atomics per rank, at the price of one more hop.
+// Mode 0 measured faster with 2 ranks, mode 1 with 8.
+__device__ __forceinline__ void ll_arrive_on_peers(const LLParams& P, const PeerPtrs& peers, int channel,
+                                                   int* state, unsigned int grid_ctas) {
+  __shared__ unsigned int s_add;
   __syncthreads();
-  if (threadIdx.x < P.R) {
+  if (P.signal_mode == 0) {
+    if (threadIdx.x == 0) s_add = 1u;
+  } else if (threadIdx.x == 0) {
+    fence_acq_rel_sys();
+    const unsigned int prev = atomicAdd(reinterpret_cast<unsigned int*>(state + 4), 1u);
+    const bool last = ((prev + 1u) % grid_ctas) == 0u;
+    // the last CTA acquires what the others published before they counted themselves
+    if (last) asm volatile("fence.acq_rel.gpu;" ::: "memory");
+    s_add = last ? grid_ctas : 0u;
+  }
+  __syncthreads();
+  const unsigned int add = s_add;
+  if (add != 0u && threadIdx.x < P.R) {
     unsigned int* ctr = reinterpret_cast<unsigned int*>(peers.base[threadIdx.x] + P.flags) + channel * kMaxRanks + P.rank;
-    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ctr), "r"(add) : "memory");
   }
 }
 
@@ -147,7 +167,7 @@ ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
     }
     __syncthreads();
   }
-  ll_arrive_on_peers(P, peers, kChLLDispatch);
+  ll_arrive_on_peers(P, peers, kChLLDispatch, state, gridDim.x);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -270,7 +290,7 @@ ll_combine_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
         if (v0 + u * 32 < nv) st_global_v4(dst + ((size_t)(v0 + u * 32) << 4), buf[u]);
     }
   }
-  ll_arrive_on_peers(P, peers, kChLLCombine);
+  ll_arrive_on_peers(P, peers, kChLLCombine, state, gridDim.x * gridDim.y);
 }
 
 // combine, receive half: out[t] = sum_k w[t,k] * slot(t,k) over k with topk_idx[t,k] >= 0.

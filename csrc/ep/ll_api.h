@@ -19,10 +19,11 @@ struct LLParams {
   long long recv_tag[2];      // int [El][R][M]  epoch in which the slot was written
   int G;                      // CTAs of EVERY dispatch-send launch (same on all ranks)
   int Gc;                     // CTAs of EVERY combine-send launch (multiple of El)
+  int signal_mode;            // 0: every send CTA signals every peer; 1: the last CTA does (see ll.cu)
   unsigned long long timeout_ns;
 };
 
-// `state`: device int[4] per op (see ll.cu). `send_cnt`: device int[2*E], zero-initialised once.
+// `state`: device int[6] per op (see ll.cu). `send_cnt`: device int[2*E], zero-initialised once.
 void launch_ll_dispatch_send(const LLParams& P, const PeerPtrs& peers, const char* x,
                              const long long* topk_idx, int* send_cnt, int* state, int* status,
                              cudaStream_t st);

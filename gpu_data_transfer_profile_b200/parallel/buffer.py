@@ -568,6 +568,11 @@ class Buffer:
         """Nothing to clean: flags are epochs and regions are double-buffered."""
 
     LL_SPLIT = 4          # combine-send CTAs per local expert
+    # How a low-latency send kernel tells the peers that it is done: 0 = every CTA adds 1 to its
+    # arrival counter on every peer, 1 = CTAs count themselves locally and the last one adds the
+    # grid size on every peer. None = by group size (mode 0 measured faster with 2 ranks, where a
+    # peer takes few remote atomics; mode 1 with 8). Must be the same on every rank.
+    ll_signal_mode: Optional[int] = None
 
     def _ll_state(self, E: int, K: int, H: int, M: int):
         key = (E, K, H, M)
@@ -586,7 +591,7 @@ class Buffer:
             if self._ll_words is None:
                 # device-resident op state (epochs and arrival targets); lives as long as the buffer
                 # because the peers' arrival counters are cumulative
-                self._ll_words = torch.zeros(8, dtype=torch.int32, device=dev)
+                self._ll_words = torch.zeros(12, dtype=torch.int32, device=dev)
             self._ll = dict(key=key, carve=carve, words=self._ll_words,
                             send_cnt=torch.zeros(2 * E, dtype=torch.int32, device=dev))
             self._carve = None
@@ -598,7 +603,8 @@ class Buffer:
         R = self.group_size
         El = E // R
         return [self.rank, R, E, El, K, H, M, T, int(fp8), 0, *c.count, *c.recv_x, *c.recv_scales,
-                *c.recv_src, *c.comb_x, self._timeout_ns(), *c.recv_tag, min(M, 128), El * Buffer.LL_SPLIT]
+                *c.recv_src, *c.comb_x, self._timeout_ns(), *c.recv_tag, min(M, 128), El * Buffer.LL_SPLIT,
+                (1 if R >= 8 else 0) if Buffer.ll_signal_mode is None else int(Buffer.ll_signal_mode)]
 
     def _ll_dispatch_send(self, x, topk_idx, M, E, use_fp8):
         if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
@@ -612,7 +618,7 @@ class Buffer:
         K = topk_idx.shape[1]
         st = self._ll_state(E, K, H, M)
         pv = self._ll_params(st, T, use_fp8)
-        self.C.ll_dispatch_send(pv, self.peers, x, topk_idx, st["send_cnt"], st["words"][0:4], self.status_ptr)
+        self.C.ll_dispatch_send(pv, self.peers, x, topk_idx, st["send_cnt"], st["words"][0:6], self.status_ptr)
         return dict(st=st, pv=pv, T=T, H=H, K=K, E=E, M=M, fp8=use_fp8, topk_idx=topk_idx, x=x)
 
     def _ll_dispatch_recv(self, d):
@@ -629,7 +635,7 @@ class Buffer:
         out_count = torch.empty((El,), dtype=torch.int32, device=dev)
         out_range = torch.empty((El, R, 2), dtype=torch.int32, device=dev)
         self.C.ll_dispatch_recv(d["pv"], self.region.local_ptr, out_x, out_s, out_src, out_count, out_range,
-                                d["st"]["words"][0:4], self.status_ptr, 4)
+                                d["st"]["words"][0:6], self.status_ptr, 4)
         handle = (out_src, out_range, M, H, d["E"], out_count, d["K"])
         return ((out_x, out_s) if d["fp8"] else out_x), out_count, handle
 
@@ -664,7 +670,7 @@ class Buffer:
         if x.dtype != torch.bfloat16 or not x.is_contiguous():
             raise ValueError("low-latency combine takes a contiguous bf16 [E_local, R*M, hidden] tensor")
         pv = self._ll_params(st, 0, False)
-        self.C.ll_combine_send(pv, self.peers, x, src_info, count, st["words"][4:8], self.status_ptr)
+        self.C.ll_combine_send(pv, self.peers, x, src_info, count, st["words"][6:12], self.status_ptr)
         return dict(st=st, H=H)
 
     def _ll_combine_recv(self, c, topk_idx, topk_weights, out=None):
@@ -674,7 +680,7 @@ class Buffer:
         if out is None:
             out = torch.empty((T, c["H"]), dtype=torch.bfloat16, device=self.device)
         w = topk_weights.to(torch.float32).contiguous() if topk_weights is not None else None
-        self.C.ll_combine_recv(pv, self.region.local_ptr, topk_idx, w, out, c["st"]["words"][4:8],
+        self.C.ll_combine_recv(pv, self.region.local_ptr, topk_idx, w, out, c["st"]["words"][6:12],
                                self.status_ptr, max(Buffer.num_sms * 4, 1))
         return out
 

@@ -23,11 +23,14 @@ def _unpack(src):
     return (src >> 24) & 0xff, (src & 0xffffff) >> 5, src & 31
 
 
+# signal_mode: 0 = every send CTA adds 1 on every peer's arrival counter, 1 = the last CTA adds the grid size
+@pytest.mark.parametrize("signal_mode", [0, 1])
 @pytest.mark.parametrize("R,T,H,E,K,fp8", [(1, 16, 256, 4, 2, False), (2, 32, 512, 8, 2, True),
                                            (4, 48, 1024, 16, 4, True), (8, 24, 512, 32, 8, False)])
-def test_low_latency_round_trip(R, T, H, E, K, fp8):
+def test_low_latency_round_trip(R, T, H, E, K, fp8, signal_mode, monkeypatch):
     from gpu_data_transfer_profile_b200.parallel.buffer import Buffer
     from gpu_data_transfer_profile_b200.parallel.local import LocalGroup
+    monkeypatch.setattr(Buffer, "ll_signal_mode", signal_mode)
     M = 64
     g = LocalGroup(R, Buffer.get_low_latency_nvl_size_hint(M, H, R, E, K), timeout_s=2.0)
     try:
