@@ -90,12 +90,17 @@ def main() -> int:
         dh = torch.randn(rows, 2 * F, device=dev).to(torch.bfloat16)
         dy = torch.randn(rows, H, device=dev).to(torch.bfloat16)
         dw1, dw2 = torch.empty_like(w1), torch.empty_like(w2)
+        dact = torch.empty(rows, F, dtype=torch.bfloat16, device=dev)
         for form in (["cta", "pair"] if args.form == "both" else [args.form]):
             pair = form == "pair"
             tag = "_pair" if pair else ""
             fns["wgrad1_tcgen05" + tag] = lambda pair=pair: G.grouped_wgrad(dh, x, off, out=dw1, pair=pair)
             fns["wgrad2_tcgen05" + tag] = lambda pair=pair: G.grouped_wgrad(dy, act, off, out=dw2, pair=pair)
             flops["wgrad1_tcgen05" + tag], flops["wgrad2_tcgen05" + tag] = f1, f2
+            # data gradients: the forward weights read in place as an N-major operand
+            fns["dgrad1_tcgen05" + tag] = lambda pair=pair: G.grouped_gemm(dh, w1, off, out=out, pair=pair, w_kn=True)
+            fns["dgrad2_tcgen05" + tag] = lambda pair=pair: G.grouped_gemm(dy, w2, off, out=dact, pair=pair, w_kn=True)
+            flops["dgrad1_tcgen05" + tag], flops["dgrad2_tcgen05" + tag] = f1, f2
         if not args.skip_torch:
             def torch_wgrad(gg, xx, dw):
                 r = 0
