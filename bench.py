@@ -183,7 +183,8 @@ def main() -> int:
                        "zipf_s": args.zipf, "l2": "flushed between steps (252 MiB write)",
                        "receive": "zero-copy views of the symmetric receive region, "
                                   + ("sized by a host read of the count" if args.host_count else "num_worst_tokens = world x tokens (no host sync)"),
-                       "num_sms_knob": Buffer.num_sms},
+                       "num_sms_knob": Buffer.num_sms,
+                       "host_cpus_allowed": len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else None},
             "tokens_per_s": round(total_tokens / (ms * 1e-3), 1),
             "nvlink_gbs_per_rank": round(nv_bytes_max / (ms * 1e-3) / 1e9, 2),
             "nvlink_roofline_frac_of_770GBs": round(nv_bytes_max / 770e9 / (ms * 1e-3), 4) if world > 1 else None,

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import os
 import sys
-from typing import Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -22,12 +22,55 @@ def env_rank_info() -> Tuple[int, int, int]:
     return int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
 
 
+def parse_cpulist(text: str) -> List[int]:
+    """'0-3,8,10-11' (the kernel's cpulist format) -> [0, 1, 2, 3, 8, 10, 11]."""
+    out: List[int] = []
+    for part in text.strip().split(","):
+        part = part.strip()
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        out.extend(range(int(lo), int(hi or lo) + 1))
+    return out
+
+
+def gpu_local_cpus(device_index: int) -> List[int]:
+    """CPUs that the kernel reports as local to the GPU (its PCIe root's NUMA node); [] if unknown."""
+    try:
+        pr = torch.cuda.get_device_properties(device_index)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/local_cpulist") as f:
+            return parse_cpulist(f.read())
+    except Exception:
+        return []
+
+
+def bind_to_gpu_cpus(device_index: int) -> List[int]:
+    """Restrict THIS process to the CPUs local to its GPU, so that the pinned host buffers it
+    allocates afterwards (first touch) sit on the GPU's NUMA node and host<->device copies do
+    not cross the socket interconnect. Only the calling process's CPU affinity changes. Returns
+    the CPUs now allowed ([] = left as it was; B200EP_BIND_CPUS=0 switches this off)."""
+    if os.environ.get("B200EP_BIND_CPUS", "1") == "0" or not hasattr(os, "sched_setaffinity"):
+        return []
+    try:
+        allowed = set(os.sched_getaffinity(0))
+        want = sorted(allowed & set(gpu_local_cpus(device_index)))
+        if len(want) < 4 or len(want) == len(allowed):      # unknown, already bound, or too few cores to be worth it
+            return []
+        os.sched_setaffinity(0, want)
+        return want
+    except Exception:
+        return []
+
+
 def init_distributed(backend: Optional[str] = None) -> Tuple[int, int, int]:
     """Initialise torch.distributed when launched by torchrun; single process otherwise."""
     rank, world, local = env_rank_info()
     use_cuda = torch.cuda.is_available()
     if use_cuda:
         torch.cuda.set_device(local % max(torch.cuda.device_count(), 1))
+        if world > 1:
+            bind_to_gpu_cpus(torch.cuda.current_device())
     if "RANK" in os.environ and not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29500")

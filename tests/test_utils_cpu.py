@@ -142,3 +142,15 @@ def test_deep_ep_compat_module_exposes_the_api_the_reference_imports():
         sys.path.pop(0)
         sys.modules.pop("deep_ep", None)
         sys.modules.pop("deep_ep.utils", None)
+
+
+def test_parse_cpulist_and_binding_is_a_no_op_without_a_gpu():
+    from gpu_data_transfer_profile_b200.utils import dist as D
+    assert D.parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    assert D.parse_cpulist("") == []
+    assert D.parse_cpulist("5") == [5]
+    import os
+    before = os.sched_getaffinity(0)
+    assert D.gpu_local_cpus(0) == []            # no GPU here: nothing is known, nothing changes
+    assert D.bind_to_gpu_cpus(0) == []
+    assert os.sched_getaffinity(0) == before
