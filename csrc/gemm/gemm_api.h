@@ -20,6 +20,8 @@ struct GemmParams {
   void* out;              // bf16 [rows, out_ld]           (plain / swiglu)
   long long out_ld;
   const float* row_prob;  // f32 [rows] or null            (swiglu)
+  void* pre_out;          // bf16 [rows, pre_ld] or null   (swiglu: also store the pre-activation [gate | linear])
+  long long pre_ld;
   const int2* recv_meta;  // {slot at source, source rank} (combine)
   long long comb_off;     // offset of the combine region in every rank's symmetric buffer
   int slot_cap, R, rank;

@@ -303,6 +303,39 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
         __syncwarp();
+        if (EPI == EPI_SWIGLU && p.pre_out != nullptr) {
+          // training forward: also keep the pre-activation [gate | linear] (bf16) for the backward pass
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t v[32];
+              tmem_ld32(t_addr + half * 128 + c * 64 + h * 32, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                packed[h * 16 + i] = *reinterpret_cast<uint32_t*>(&hh);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              srow[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int step = 0; step < 8; ++step) {
+              const int r = step * 4 + (lane >> 3);
+              const int seg = lane & 7;
+              if ((q * 32 + r) < tl.valid_rows && (col0 + seg * 8) < p.N_out) {
+                const uint4 val = *reinterpret_cast<const uint4*>(my_smem + r * EPI_ROW_BYTES + seg * 16);
+                char* dst = reinterpret_cast<char*>(p.pre_out) +
+                            ((size_t)(tl.row0 + q * 32 + r) * p.pre_ld + (size_t)half * p.N + col0 + seg * 8) * 2;
+                st_global_v4(dst, val);
+              }
+            }
+            __syncwarp();
+          }
+        }
       }
       fence_before_sync();
       __syncwarp();

@@ -101,6 +101,15 @@ def main() -> int:
             fns["dgrad1_tcgen05" + tag] = lambda pair=pair: G.grouped_gemm(dh, w1, off, out=out, pair=pair, w_kn=True)
             fns["dgrad2_tcgen05" + tag] = lambda pair=pair: G.grouped_gemm(dy, w2, off, out=dact, pair=pair, w_kn=True)
             flops["dgrad1_tcgen05" + tag], flops["dgrad2_tcgen05" + tag] = f1, f2
+        # training forward of fc1: one kernel that also stores the pre-activation, vs plain fc1 + SwiGLU kernel
+        hpre = torch.empty(rows, 2 * F, dtype=torch.bfloat16, device=dev)
+
+        def fc1_train_separate():
+            G.grouped_gemm(x, w1, off, out=hpre)
+            return G.swiglu_fwd(hpre, prob)
+        fns["fc1_train_fused_tcgen05"] = lambda: G.grouped_gemm_swiglu(x, w1, off, prob, out=act, pre_out=hpre)
+        fns["fc1_train_separate_tcgen05"] = fc1_train_separate
+        flops["fc1_train_fused_tcgen05"] = flops["fc1_train_separate_tcgen05"] = f1
         if not args.skip_torch:
             def torch_wgrad(gg, xx, dw):
                 r = 0

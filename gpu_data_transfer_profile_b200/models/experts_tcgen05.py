@@ -54,8 +54,8 @@ def _wgrad(dy, a, counts, out_shape, expert_off=None):
 
 
 class _GroupedMLP(torch.autograd.Function):
-    """Training path. SwiGLU: fc1 (tcgen05, plain epilogue, keeps the pre-activation h) -> fused
-    swiglu x prob kernel -> fc2 (tcgen05). Backward: fused swiglu backward kernel, both dgrads on
+    """Training path. SwiGLU: fc1 (tcgen05; the epilogue applies SwiGLU x prob AND stores the
+    pre-activation h for backward) -> fc2 (tcgen05). Backward: fused swiglu backward kernel, both dgrads on
     the tcgen05 grouped GEMM (weights read in place, N-major), both wgrads on the tcgen05
     ragged-reduction kernel."""
 
@@ -64,8 +64,9 @@ class _GroupedMLP(torch.autograd.Function):
         ctx.counts, ctx.activation = counts, activation
         ctx.off = expert_off
         if activation == "swiglu":
-            h = G.grouped_gemm(x, w1, expert_off)
-            act = G.swiglu_fwd(h, probs)
+            # one kernel: fc1, SwiGLU x prob in the epilogue, and the pre-activation kept for backward
+            h = torch.empty((x.shape[0], w1.shape[1]), dtype=x.dtype, device=x.device)
+            act = G.grouped_gemm_swiglu(x, w1, expert_off, probs, pre_out=h)
             y = G.grouped_gemm(act, w2, expert_off)
             ctx.save_for_backward(x, w1, w2, probs, h, act)
             return y
@@ -99,8 +100,8 @@ class _GroupedMLPFusedCombine(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w1, w2, probs, expert_off, counts, buffer, handle):
-        h = G.grouped_gemm(x, w1, expert_off)
-        act = G.swiglu_fwd(h, probs)
+        h = torch.empty((x.shape[0], w1.shape[1]), dtype=x.dtype, device=x.device)
+        act = G.grouped_gemm_swiglu(x, w1, expert_off, probs, pre_out=h)
         out = buffer.fused_fc2_combine(act, w2, handle)
         ctx.save_for_backward(x, w1, w2, probs, h, act)
         ctx.counts, ctx.off, ctx.buffer, ctx.handle = counts, expert_off, buffer, handle

@@ -54,19 +54,22 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, expert_off: torch.Tensor, *, 
     if out is None:
         out = torch.empty((a.shape[0], w.shape[2] if w_kn else w.shape[1]), dtype=torch.bfloat16, device=a.device)
     _ext.load().grouped_gemm(a, w, expert_off, PLAIN, out, None, None, [], 0, 0, 0, -1, 0, None, 0,
-                             ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes), w_kn)
+                             ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes), w_kn, None)
     return out
 
 
 def grouped_gemm_swiglu(a: torch.Tensor, w: torch.Tensor, expert_off: torch.Tensor, row_prob: Optional[torch.Tensor],
                         *, out: Optional[torch.Tensor] = None, ctas: int = 0,
-                        pair: Optional[bool] = None, band_bytes: Optional[int] = None) -> torch.Tensor:
-    """w bf16 [E, 2F, K] (gate rows first): out[r] = silu(a[r] @ Wg.T) * (a[r] @ Wl.T) * row_prob[r] -> bf16 [rows,F]"""
+                        pair: Optional[bool] = None, band_bytes: Optional[int] = None,
+                        pre_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """w bf16 [E, 2F, K] (gate rows first): out[r] = silu(a[r] @ Wg.T) * (a[r] @ Wl.T) * row_prob[r] -> bf16 [rows,F].
+    pre_out (bf16 [rows, 2F]): if given, the same kernel also stores the pre-activation a[r] @ W.T
+    there (what the backward pass needs), so the training forward needs no separate activation kernel."""
     F = w.shape[1] // 2
     if out is None:
         out = torch.empty((a.shape[0], F), dtype=torch.bfloat16, device=a.device)
     _ext.load().grouped_gemm(a, w, expert_off, SWIGLU, out, row_prob, None, [], 0, 0, 0, -1, 0, None, 0,
-                             ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes), False)
+                             ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes), False, pre_out)
     return out
 
 
@@ -77,7 +80,7 @@ def grouped_gemm_combine(a: torch.Tensor, w: torch.Tensor, expert_off: torch.Ten
     """fc2 with the combine send fused into the epilogue: row r of a @ w[e].T is stored into slot
     recv_meta[r,0] of rank recv_meta[r,1]'s combine region (peer LSU stores)."""
     _ext.load().grouped_gemm(a, w, expert_off, COMBINE, None, None, recv_meta, list(peers), comb_off, slot_cap,
-                             rank, signal_flag_off, epoch, counter, status_ptr, ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes), False)
+                             rank, signal_flag_off, epoch, counter, status_ptr, ctas or _ctas(a.device), _pair(pair), _band_rows(a.shape[1], band_bytes), False, None)
 
 
 def grouped_wgrad(g: torch.Tensor, x: torch.Tensor, expert_off: torch.Tensor, *, out: Optional[torch.Tensor] = None,

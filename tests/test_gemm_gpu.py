@@ -89,6 +89,25 @@ def test_grouped_wgrad(counts, M, N, pair):
         r += c
 
 
+@pytest.mark.parametrize("pair", [False, True])
+def test_grouped_gemm_swiglu_also_stores_pre_activation(pair):
+    from gpu_data_transfer_profile_b200.ops import gemm as G
+    torch.manual_seed(6)
+    counts, F, K = [300, 1, 0, 215], 384, 320
+    rows = sum(counts)
+    a = torch.randn(rows, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(len(counts), 2 * F, K, device="cuda") * 0.1).to(torch.bfloat16)
+    prob = torch.rand(rows, device="cuda")
+    pre = torch.full((rows + 3, 2 * F), 5.0, dtype=torch.bfloat16, device="cuda")
+    out = G.grouped_gemm_swiglu(a, w, G.offsets_from_counts(counts, "cuda"), prob, pair=pair, pre_out=pre)
+    torch.cuda.synchronize()
+    fc1 = _ref(a, w, counts)
+    torch.testing.assert_close(pre[:rows].float(), fc1, atol=0.06, rtol=2e-2)
+    assert bool((pre[rows:] == 5.0).all())
+    ref = torch.nn.functional.silu(fc1[:, :F]) * fc1[:, F:] * prob[:, None]
+    torch.testing.assert_close(out.float(), ref, atol=0.06, rtol=3e-2)
+
+
 def test_grouped_gemm_rejects_bad_shapes():
     from gpu_data_transfer_profile_b200.ops import gemm as G
     a = torch.zeros(8, 36, device="cuda", dtype=torch.bfloat16)
