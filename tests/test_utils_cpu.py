@@ -154,3 +154,34 @@ def test_parse_cpulist_and_binding_is_a_no_op_without_a_gpu():
     assert D.gpu_local_cpus(0) == []            # no GPU here: nothing is known, nothing changes
     assert D.bind_to_gpu_cpus(0) == []
     assert os.sched_getaffinity(0) == before
+
+
+def test_low_latency_regions_are_aligned_disjoint_and_inside_the_size_hint():
+    from gpu_data_transfer_profile_b200.parallel.buffer import _LLCarve
+    from gpu_data_transfer_profile_b200.parallel.config import FIXED_BYTES, REGION_ALIGN
+    for R, E, M, H, K in [(1, 4, 16, 256, 2), (2, 8, 64, 512, 2), (8, 256, 128, 7168, 8), (4, 16, 48, 1024, 4)]:
+        need = _LLCarve.required_bytes(R, E, M, H, K)
+        c = _LLCarve(need, R, E, M, H, K)
+        sizes = _LLCarve._sizes(R, E, M, H, K)
+        spans = []
+        for name, sz in sizes.items():
+            for p in range(2):
+                off = getattr(c, name)[p]
+                assert off % REGION_ALIGN == 0 and off >= FIXED_BYTES
+                spans.append((off, off + sz))
+        spans.sort()
+        for (a0, a1), (b0, _) in zip(spans, spans[1:]):
+            assert a1 <= b0                                  # no two regions (either parity) overlap
+        assert spans[-1][1] <= need
+        assert c.count[0] < c.count[1] < FIXED_BYTES          # per-parity count rows live in the control area
+        import pytest
+        with pytest.raises(ValueError):
+            _LLCarve(need - REGION_ALIGN - 1, R, E, M, H, K)
+
+
+def test_gemm_band_height_follows_the_reduction_length():
+    from gpu_data_transfer_profile_b200.ops import gemm as G
+    assert G._band_rows(4096, 32 << 20) == 4096               # 32 MiB of 8 KiB rows
+    assert G._band_rows(14336, 32 << 20) == 1024              # rounded down to a multiple of 256 rows
+    assert G._band_rows(1 << 20, 32 << 20) == 256             # never below one 256-row tile
+    assert G._band_rows(4096) == G._band_rows(4096, G.BAND_BYTES)
