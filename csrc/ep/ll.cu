@@ -27,6 +27,16 @@ constexpr int kLLThreads = 256;  // 8 warps work on one row together
 // No kernel ever reads a word that another CTA of the same launch writes.
 struct LLTick { int epoch, target; };
 
+// First statement of every kernel below. When a kernel is launched with programmatic stream
+// serialisation (P.pdl), its CTAs may be placed on the SMs while the previous kernel of the stream
+// is still running: `griddepcontrol.wait` holds them until that kernel has completed and its
+// writes are visible, so only the launch latency overlaps, never the work. Each kernel at once
+// lets ITS successor do the same. Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void ll_stream_order() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ LLTick ll_tick_send(int* st, int grid_ctas) {
   __shared__ int s_e, s_t;
   if (threadIdx.x == 0) {
@@ -88,6 +98,7 @@ ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
   __shared__ char* s_dst[kMaxItemsPerToken];
   __shared__ float* s_scl[kMaxItemsPerToken];
   __shared__ int s_n;
+  ll_stream_order();
   const LLTick tk = ll_tick_send(state, gridDim.x);
   const int epoch = tk.epoch;
   const int par = epoch & 1;
@@ -182,6 +193,7 @@ ll_dispatch_recv_kernel(LLParams P, char* self_base, char* __restrict__ out_x,
   __shared__ int s_off[kMaxRanks + 1];
   __shared__ int s_cnt[kMaxRanks];
   __shared__ int ok;
+  ll_stream_order();
   const LLTick tk = ll_tick_recv(state);
   const int epoch = tk.epoch;
   const int par = epoch & 1;
@@ -256,6 +268,7 @@ __global__ void __launch_bounds__(kLLThreads)
 ll_combine_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
                        const int* __restrict__ src_info, const int* __restrict__ count,
                        int* state, int* status) {
+  ll_stream_order();
   const LLTick tk = ll_tick_send(state, gridDim.x * gridDim.y);
   const int par = tk.epoch & 1;
   const int el = blockIdx.x;
@@ -300,6 +313,7 @@ ll_combine_recv_kernel(LLParams P, char* self_base, const long long* __restrict_
                        int* state, int* status) {
   __shared__ float s_w[kMaxItemsPerToken];
   __shared__ int ok;
+  ll_stream_order();
   const LLTick tk = ll_tick_recv(state);
   const int par = tk.epoch & 1;
   if (threadIdx.x == 0) ok = 1;
@@ -353,28 +367,42 @@ ll_combine_recv_kernel(LLParams P, char* self_base, const long long* __restrict_
 // ---- launchers -------------------------------------------------------------------------
 // The dispatch send grid is ALWAYS P.G CTAs and the combine send grid ALWAYS (El, P.Gc / El):
 // receivers count arrivals, so the number of CTAs must be the same on every rank.
+template <typename... KArgs>
+static void ll_launch(void (*kern)(KArgs...), dim3 grid, bool pdl, cudaStream_t st, KArgs... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kLLThreads, 1, 1);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 void launch_ll_dispatch_send(const LLParams& P, const PeerPtrs& peers, const char* x,
                              const long long* topk_idx, int* send_cnt, int* state, int* status,
                              cudaStream_t st) {
-  ll_dispatch_send_kernel<<<P.G, kLLThreads, 0, st>>>(P, peers, x, topk_idx, send_cnt, state, status);
+  ll_launch(ll_dispatch_send_kernel, dim3(P.G), P.pdl != 0, st, P, peers, x, topk_idx, send_cnt, state, status);
 }
 void launch_ll_dispatch_recv(const LLParams& P, char* self_base, char* out_x, float* out_scales,
                              int* out_src, int* out_count, int* out_range, int* state,
                              int* status, int split, cudaStream_t st) {
   if (split < 1) split = 1;
-  ll_dispatch_recv_kernel<<<dim3(P.El, split), kLLThreads, 0, st>>>(
-      P, self_base, out_x, out_scales, out_src, out_count, reinterpret_cast<int2*>(out_range), state, status);
+  ll_launch(ll_dispatch_recv_kernel, dim3(P.El, split), P.pdl != 0, st, P, self_base, out_x, out_scales, out_src,
+            out_count, reinterpret_cast<int2*>(out_range), state, status);
 }
 void launch_ll_combine_send(const LLParams& P, const PeerPtrs& peers, const char* x, const int* src_info,
                             const int* count, int* state, int* status, cudaStream_t st) {
-  ll_combine_send_kernel<<<dim3(P.El, P.Gc / P.El), kLLThreads, 0, st>>>(P, peers, x, src_info, count, state, status);
+  ll_launch(ll_combine_send_kernel, dim3(P.El, P.Gc / P.El), P.pdl != 0, st, P, peers, x, src_info, count, state, status);
 }
 void launch_ll_combine_recv(const LLParams& P, char* self_base, const long long* topk_idx,
                             const float* topk_w, char* out, int* state, int* status,
                             int blocks, cudaStream_t st) {
   int g = P.T < blocks ? P.T : blocks;
   if (g < 1) g = 1;
-  ll_combine_recv_kernel<<<g, kLLThreads, 0, st>>>(P, self_base, topk_idx, topk_w, out, state, status);
+  ll_launch(ll_combine_recv_kernel, dim3(g), P.pdl != 0, st, P, self_base, topk_idx, topk_w, out, state, status);
 }
 
 }  // namespace b200ep

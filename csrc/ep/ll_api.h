@@ -20,6 +20,7 @@ struct LLParams {
   int G;                      // CTAs of EVERY dispatch-send launch (same on all ranks)
   int Gc;                     // CTAs of EVERY combine-send launch (multiple of El)
   int signal_mode;            // 0: every send CTA signals every peer; 1: the last CTA does (see ll.cu)
+  int pdl;                    // 1: launch with programmatic stream serialisation (launch latencies overlap)
   unsigned long long timeout_ns;
 };
 

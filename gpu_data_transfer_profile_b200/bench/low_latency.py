@@ -31,6 +31,8 @@ def main() -> int:
     ap.add_argument("--warmup-iters", type=int, default=10)
     ap.add_argument("--benchmark-iters", type=int, default=100)
     ap.add_argument("--num-sms", type=int, default=32)
+    ap.add_argument("--overlap-launches", action="store_true",
+                    help="launch the kernels with programmatic stream serialisation (launch latencies overlap)")
     ap.add_argument("--signal-mode", type=int, choices=(0, 1), default=None,
                     help="0: every send CTA signals every peer; 1: the last CTA does; default: by group size")
     ap.add_argument("--seed", type=int, default=1234)
@@ -44,6 +46,7 @@ def main() -> int:
     fp8 = not a.no_fp8
     Buffer.set_num_sms(a.num_sms)
     Buffer.ll_signal_mode = a.signal_mode
+    Buffer.ll_overlap_launches = a.overlap_launches
     lw = None if D.is_dist() else LocalWorld.make(1, dev)[0]
     buf = Buffer(group, Buffer.get_low_latency_nvl_size_hint(M, H, a.ep, E, K), 0, low_latency_mode=True, world=lw)
     x = torch.randn(T, H, generator=torch.Generator().manual_seed(a.seed + rank)).to(torch.bfloat16).to(dev)

@@ -74,9 +74,12 @@ def test_low_latency_round_trip(R, T, H, E, K, fp8, signal_mode, monkeypatch):
         g.destroy()
 
 
-def test_low_latency_cuda_graph_replay():
+# overlap: the kernels are launched with programmatic stream serialisation (captured as such in the graph)
+@pytest.mark.parametrize("overlap", [False, True])
+def test_low_latency_cuda_graph_replay(overlap, monkeypatch):
     from gpu_data_transfer_profile_b200.parallel.buffer import Buffer
     from gpu_data_transfer_profile_b200.parallel.local import LocalGroup
+    monkeypatch.setattr(Buffer, "ll_overlap_launches", overlap)
     R, T, H, E, K, M = 1, 32, 512, 8, 4, 32
     g = LocalGroup(R, Buffer.get_low_latency_nvl_size_hint(M, H, R, E, K), timeout_s=2.0)
     try:
