@@ -5,8 +5,11 @@
 //  * Cross-GPU bytes move only by LSU loads/stores on peer-mapped pointers
 //    (or multimem); TMA is used on this GPU's own memory only.
 //  * No wait is unbounded. A wait that runs out records a code in a status
-//    word (host-visible pinned memory) and returns false; callers then skip the
-//    dependent work and return, so the context stays usable.
+//    block and returns false; callers then skip the dependent work and return, so
+//    the context stays usable. The status block is device memory (word 0 = first
+//    code recorded); words 2-3 may hold the device-visible address of a pinned
+//    host word that receives a copy of the code, so that the host can notice a
+//    fault without synchronising the device.
 //  * Flags are monotonically increasing epochs, never reset: a waiter waits for
 //    flag >= epoch. Payload regions are double-buffered by epoch parity, which
 //    makes a start-of-op barrier unnecessary (a rank can never run two epochs
@@ -39,9 +42,24 @@ struct PeerPtrs {
   char* base[kMaxRanks];
 };
 
+// Cumulative 32-bit counters (low-latency arrival counters) are compared modulo 2^32:
+// `have` has reached `want` when it is at most 2^31 - 1 increments ahead of it. A signed
+// `have >= want` would turn false->true at the 0x7fffffff -> 0x80000000 wrap of `want`.
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
+inline bool counter_reached(uint32_t have, uint32_t want) {
+  return static_cast<int32_t>(have - want) >= 0;
+}
+
 #ifdef __CUDACC__
 __device__ __forceinline__ void set_status(int* status, int code) {
-  if (status != nullptr) atomicCAS_system(status, 0, code);
+  if (status == nullptr) return;
+  if (atomicCAS_system(status, 0, code) == 0) {
+    // first error of this block: mirror it to the host word, if one is registered
+    int* host = *reinterpret_cast<int* volatile*>(status + 2);
+    if (host != nullptr) *reinterpret_cast<volatile int*>(host) = code;
+  }
 }
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -79,6 +97,20 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int want, uint64_t
   // The iteration cap bounds the loop even if the timer misbehaves.
   for (uint64_t it = 0; it < (1ull << 34); ++it) {
     if (ld_acquire_sys(flag) >= want) return true;
+    if ((it & 63) == 63 && globaltimer_ns() - t0 > timeout_ns) break;
+    __nanosleep(32);
+  }
+  set_status(status, code);
+  return false;
+}
+
+// Same bounded wait for a cumulative counter that may wrap around 2^32.
+__device__ __forceinline__ bool wait_counter_reached(const int* flag, uint32_t want, uint64_t timeout_ns,
+                                                     int* status, int code) {
+  if (counter_reached((uint32_t)ld_acquire_sys(flag), want)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint64_t it = 0; it < (1ull << 34); ++it) {
+    if (counter_reached((uint32_t)ld_acquire_sys(flag), want)) return true;
     if ((it & 63) == 63 && globaltimer_ns() - t0 > timeout_ns) break;
     __nanosleep(32);
   }

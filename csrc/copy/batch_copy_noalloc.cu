@@ -1,5 +1,6 @@
-// See batch_copy_noalloc.h for the contract. The kernel is the batched copy kernel of
-// batch_copy.cu with its descriptor table taken from the static array below.
+// See batch_copy_noalloc.h for the contract. The kernel is `batched_copy_kernel` of
+// batch_copy.cu (launched through `launch_batched_copy`), reading its descriptor table from
+// the static array below instead of from allocated memory.
 #include <mutex>
 #include "../common.cuh"
 #include "batch_copy_noalloc.h"
@@ -9,24 +10,6 @@ namespace b200ep {
 
 // The scratch: lives in the library image, one instance per GPU that loads it.
 static __device__ __align__(256) CopyDesc g_noalloc_table[B200EP_NOALLOC_MAX_COPIES];
-
-__global__ void batched_copy_noalloc_kernel(const CopyDesc* __restrict__ desc, int n) {
-  const int c = blockIdx.y;
-  if (c >= n) return;
-  const CopyDesc d = desc[c];
-  char* dst = static_cast<char*>(d.dst);
-  const char* src = static_cast<const char*>(d.src);
-  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long nth = (long long)gridDim.x * blockDim.x;
-  const bool aligned = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0;
-  if (aligned) {
-    const long long nvec = d.nbytes >> 4;
-    for (long long v = tid; v < nvec; v += nth) st_global_v4(dst + (v << 4), ld_global_v4(src + (v << 4)));
-    for (long long i = (nvec << 4) + tid; i < d.nbytes; i += nth) dst[i] = src[i];
-  } else {
-    for (long long i = tid; i < d.nbytes; i += nth) dst[i] = src[i];
-  }
-}
 
 namespace {
 constexpr int kMaxDevices = 64;
@@ -60,6 +43,13 @@ extern "C" int b200ep_batched_copy_noalloc(void* const* dsts, const void* const*
   if (n <= 0) return -2;
   if (n > B200EP_NOALLOC_MAX_COPIES) return -3;
   if (ctas_per_copy <= 0 || ctas_per_copy > 65535 || threads <= 0 || threads > 1024) return -4;
+  // The descriptor upload below reads this call's stack. Inside a stream capture it would be
+  // recorded as a copy node that keeps the stack address, and every replay would upload whatever
+  // then lies there: refuse before anything is issued.
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  cudaError_t ce = cudaStreamIsCapturing(stream, &cap);
+  if (ce != cudaSuccess) return (int)ce;
+  if (cap != cudaStreamCaptureStatusNone) return -7;
   CopyDesc host[B200EP_NOALLOC_MAX_COPIES];            // on the stack: 24 KiB, no heap
   for (int i = 0; i < n; ++i) {
     if (sizes[i] < 0 || dsts[i] == nullptr || srcs[i] == nullptr) return -5;
@@ -71,10 +61,12 @@ extern "C" int b200ep_batched_copy_noalloc(void* const* dsts, const void* const*
   const int rc = table_for_current_device(&table);
   if (rc != 0) return rc;
   // Stream-ordered upload: a previous call's kernel on this stream has finished reading the
-  // table before these bytes land. (Pageable source: the runtime has consumed `host` on return.)
+  // table before these bytes land. The source is pageable stack memory, so the runtime stages it
+  // and returns only once it has consumed `host`; the host thread waits for earlier work on the
+  // stream while it does so.
   cudaError_t e = cudaMemcpyAsync(table, host, sizeof(CopyDesc) * n, cudaMemcpyHostToDevice, stream);
   if (e != cudaSuccess) return (int)e;
-  batched_copy_noalloc_kernel<<<dim3(ctas_per_copy, n), threads, 0, stream>>>(table, n);
+  if (launch_batched_copy(table, n, ctas_per_copy, threads, stream) != 0) return -4;
   e = cudaGetLastError();
   return (int)e;
 }
@@ -88,6 +80,7 @@ extern "C" const char* b200ep_noalloc_error_string(int code) {
     case -4: return "bad launch shape (ctas_per_copy in [1,65535], threads in [1,1024])";
     case -5: return "a copy has a null pointer or a negative size";
     case -6: return "device ordinal outside the supported range";
+    case -7: return "not capturable: the stream is being captured and the descriptor upload reads caller stack memory";
     default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown error";
   }
 }

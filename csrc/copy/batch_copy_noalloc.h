@@ -22,6 +22,11 @@
 //    GPU that loads the library carries its own copy until the process exits.
 //  * The first call on a given device looks up the array's device address (with that device
 //    current) and remembers it; make that first call before starting any stream capture.
+//  * The call itself must not be made on a stream that is being captured: the descriptors are
+//    uploaded from this function's stack, which a captured copy node would keep pointing at.
+//    Such a call is refused with code -7 and nothing is issued.
+//  * The upload is a copy from pageable memory: the calling host thread waits until earlier
+//    work on `stream` has drained before the function returns.
 //  * Every call overwrites the same table, which otherwise keeps the previous call's contents.
 //    Calls issued to ONE stream are ordered and safe. Calls that may overlap on the GPU
 //    (different streams, different host threads) race on the table: serialise them yourself.

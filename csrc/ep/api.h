@@ -6,16 +6,19 @@
 
 namespace b200ep {
 
+// Ints of scratch that launch_layout needs (`partial`), for T tokens.
+int layout_scratch_ints(int T, int E, int R);
+
+// `partial`: scratch of layout_scratch_ints(...) ints; `block_counter`: one zero-initialised word
+// that the kernel leaves at zero. Outputs need no zero-fill.
 void launch_layout(const long long* topk_idx, int T, int K, int E, int R, int* per_rank,
-                   int* per_expert, bool* in_rank, int* status, cudaStream_t st);
+                   int* per_expert, bool* in_rank, int* partial, unsigned int* block_counter,
+                   int* status, cudaStream_t st);
 
 void launch_notify_send(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers,
                         const bool* is_in_rank, const long long* topk_idx,
                         const int* num_tokens_per_expert, int* item_rank, int* chunk_hist,
                         unsigned int* block_counter, int* status, cudaStream_t st);
-
-void launch_notify_wait(const EpGeom& g, const EpRegions& rg, char* self_base, const EpMeta& m,
-                        int* host_word, int* status, cudaStream_t st);
 
 void launch_wait_flags(char* self_base, long long flags_off, int channel, int R, int epoch,
                        unsigned long long timeout_ns, int* status, int code, cudaStream_t st);
@@ -23,23 +26,49 @@ void launch_wait_flags(char* self_base, long long flags_off, int channel, int R,
 void launch_barrier(const PeerPtrs& peers, long long flags_off, int rank, int R, int epoch,
                     unsigned long long timeout_ns, int* status, int wait, cudaStream_t st);
 
+// g.epoch = dispatch epoch to publish, g.epoch_wait = notify epoch to wait for (fresh dispatch),
+// g.tail_wait = 1 makes the last CTA wait for the peers' dispatch flags (never with several
+// virtual ranks on one GPU: use launch_dispatch_wait after all ranks' sends instead).
+// host_word: mapped pinned ints [0]=notify epoch served, [1]=N_recv, [2..2+El) per-expert counts.
 void launch_dispatch_send(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers,
                           const EpMeta& m, const char* x, int row_bytes_in, bool fp8, bool cached,
                           const long long* topk_idx, const float* topk_w, const int* item_rank,
                           const int* chunk_base, int* send_row, int* send_slot,
-                          unsigned int* block_counter, int* status, int blocks, cudaStream_t st,
-                          const float* scales_in = nullptr);
+                          unsigned int* block_counter, int* host_word, int* status, int blocks,
+                          cudaStream_t st, const float* scales_in = nullptr);
 
-void launch_combine_send(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers,
-                         const int* n_recv_ptr, const int* recv_meta, const char* x, int row_bytes,
-                         const float* topk_w, unsigned int* block_counter, int* status, int blocks,
-                         cudaStream_t st);
+void launch_dispatch_wait(const EpGeom& g, const EpRegions& rg, char* self_base, const EpMeta& m,
+                          int* status, cudaStream_t st);
+
+enum CombineRole : int { kCombineFused = 0, kCombineSendOnly = 1, kCombineReduceOnly = 2 };
+
+struct CombineArgs {
+  // send role
+  const int* n_recv_ptr;     // device: number of valid rows in x
+  const int2* recv_meta;     // [n_recv] {slot at source, source rank}
+  const char* x;             // [n_recv][row_bytes]
+  int row_bytes;
+  const float* topk_w;       // optional side values returned with the rows
+  const int* bnd;            // [R][kBndStride] chunk boundaries (rank mode) or nullptr
+  int* seg_count;            // [kMaxRanks*kMaxCombChunks] zero on entry, left at zero
+  unsigned int* block_counter;  // zero on entry, left at zero
+  // role selection
+  unsigned int* ticket;      // zero on entry, left at zero
+  int n_send;                // CTAs in the send role (fused launch)
+  int role;                  // CombineRole
+  // reduce role
+  const int* send_slot;      // [T][J]
+  const float* weights;      // optional [T][J]
+  char* out;                 // [T][H]
+  float* out_topk_w;         // optional [T][K]
+  int wait_mode;             // 0 none, 1 one flag per rank (channel kChCombine), 2 per-chunk flags
+};
+
+// dtype_code: 0 bf16, 1 fp16, 2 fp32 (element type of x / out).
+void launch_combine(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers, const CombineArgs& a,
+                    int dtype_code, int* status, int blocks, cudaStream_t st);
 
 void launch_signal(const PeerPtrs& peers, long long flags_off, int channel, int rank, int R,
                    int epoch, cudaStream_t st);
-
-void launch_combine_reduce(const EpGeom& g, const EpRegions& rg, char* self_base,
-                           const int* send_slot, const float* weights, char* out, float* out_topk_w,
-                           int dtype_code, int wait_epoch, int* status, int blocks, cudaStream_t st);
 
 }  // namespace b200ep

@@ -3,21 +3,27 @@
 // Replaces what the reference obtains from DeepEP's `Buffer.get_dispatch_layout` and the
 // count exchange hidden inside `Buffer.dispatch` (`DeepEP_v1/deepep_v1_dispatch.py:199-230`):
 // per-rank / per-expert token counts, `is_token_in_rank`, stable positions of every item in
-// its (source rank -> bucket) stream, an all-gather of the count vectors over NVLink with
-// plain peer stores + release flags, and the prefix sums that give every sender the exact
-// destination row of every token (so payload is stored once, in its final place).
+// its (source rank -> bucket) stream, and an all-gather of the count vectors over NVLink with
+// plain peer stores + release flags. The prefix sums that turn the gathered counts into the
+// exact destination row of every token are computed by every CTA of the dispatch kernel itself
+// (csrc/ep/dispatch.cu), so the count exchange costs one small launch, not two.
 #include "ep.cuh"
 #include "api.h"
 
 namespace b200ep {
 
 // ---------------------------------------------------------------------------------------
-// layout: counts + is_token_in_rank. One thread per token, shared-memory histograms.
+// layout: counts + is_token_in_rank. One thread per token, shared-memory histograms per CTA,
+// per-CTA partial histograms in a scratch matrix, summed by the last CTA: the outputs need no
+// zero-fill before the launch and the sums do not depend on the order of atomics.
 // ---------------------------------------------------------------------------------------
-__global__ void layout_kernel(const long long* __restrict__ topk_idx, int T, int K, int E, int R,
-                              int* __restrict__ num_tokens_per_rank,
-                              int* __restrict__ num_tokens_per_expert,
-                              bool* __restrict__ is_token_in_rank, int* status) {
+constexpr int kLayoutThreads = 256;
+
+__global__ void __launch_bounds__(kLayoutThreads)
+layout_kernel(const long long* __restrict__ topk_idx, int T, int K, int E, int R,
+              int* __restrict__ num_tokens_per_rank, int* __restrict__ num_tokens_per_expert,
+              bool* __restrict__ is_token_in_rank, int* partial, unsigned int* block_counter,
+              int* status) {
   extern __shared__ int sh[];
   int* he = sh;
   int* hr = sh + E;
@@ -43,98 +49,148 @@ __global__ void layout_kernel(const long long* __restrict__ topk_idx, int T, int
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < E; i += blockDim.x)
-    if (he[i]) atomicAdd(&num_tokens_per_expert[i], he[i]);
-  for (int i = threadIdx.x; i < R; i += blockDim.x)
-    if (hr[i]) atomicAdd(&num_tokens_per_rank[i], hr[i]);
+  const int V = E + R;
+  if (gridDim.x == 1) {
+    for (int i = threadIdx.x; i < E; i += blockDim.x) num_tokens_per_expert[i] = he[i];
+    for (int i = threadIdx.x; i < R; i += blockDim.x) num_tokens_per_rank[i] = hr[i];
+    return;
+  }
+  for (int i = threadIdx.x; i < V; i += blockDim.x) partial[(size_t)blockIdx.x * V + i] = sh[i];
+  if (!last_block_arrive(block_counter, gridDim.x)) return;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    int s = 0;
+    for (unsigned int b = 0; b < gridDim.x; ++b) s += __ldcg(&partial[(size_t)b * V + i]);
+    if (i < E) num_tokens_per_expert[i] = s;
+    else num_tokens_per_rank[i - E] = s;
+  }
+}
+
+int layout_scratch_ints(int T, int E, int R) {
+  const int blocks = T > 0 ? (T + kLayoutThreads - 1) / kLayoutThreads : 1;
+  return blocks * (E + R);
 }
 
 void launch_layout(const long long* topk_idx, int T, int K, int E, int R, int* per_rank,
-                   int* per_expert, bool* in_rank, int* status, cudaStream_t st) {
-  if (per_expert == per_rank + R) {
-    cudaMemsetAsync(per_rank, 0, sizeof(int) * (R + E), st);   // one buffer: [R rank counts | E expert counts]
-  } else {
-    cudaMemsetAsync(per_rank, 0, sizeof(int) * R, st);
-    cudaMemsetAsync(per_expert, 0, sizeof(int) * E, st);
-  }
-  if (T == 0) return;
-  const int threads = 256;
-  layout_kernel<<<(T + threads - 1) / threads, threads, (E + R) * sizeof(int), st>>>(
-      topk_idx, T, K, E, R, per_rank, per_expert, in_rank, status);
+                   int* per_expert, bool* in_rank, int* partial, unsigned int* block_counter,
+                   int* status, cudaStream_t st) {
+  const int blocks = T > 0 ? (T + kLayoutThreads - 1) / kLayoutThreads : 1;
+  layout_kernel<<<blocks, kLayoutThreads, (E + R) * sizeof(int), st>>>(
+      topk_idx, T, K, E, R, per_rank, per_expert, in_rank, partial, block_counter, status);
 }
 
 // ---------------------------------------------------------------------------------------
-// notify_send: one CTA per chunk of 32 tokens computes the stable intra-chunk rank of each
-// item and the chunk histogram; the last CTA to finish scans the histograms over chunks
-// (turning them into chunk bases), builds this rank's count vector [R rank counts | E expert
-// counts] and stores it into every peer's count matrix, then releases the notify flag.
+// notify_send: one WARP per chunk of 32 tokens (lane = token) computes the stable rank of each
+// item inside its chunk and the chunk histogram:
+//   rank mode   : for every destination rank one ballot over the chunk's tokens;
+//   expert mode : a 32-bit mask per expert in shared memory (bit = token of the chunk that
+//                 chose the expert); an item's rank is the number of lower bits.
+// The last CTA to finish scans the histograms over chunks (turning them into chunk bases),
+// builds this rank's count vector [R rank counts | E expert counts], stores it into every
+// peer's count matrix and releases the notify flag.
 // ---------------------------------------------------------------------------------------
-template <int MODE>
-__global__ void notify_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers,
-                                   const bool* __restrict__ is_in_rank,
-                                   const long long* __restrict__ topk_idx,
-                                   const int* __restrict__ num_tokens_per_expert,
-                                   int* __restrict__ item_rank, int* chunk_hist,
-                                   unsigned int* block_counter, int* status) {
-  extern __shared__ int sh[];
-  const int J = g.J, B = g.B, R = g.R, E = g.E;
-  int* items = sh;                       // [32*J]
-  int* hist = sh + kChunkTokens * J;     // [B]
-  int* vec = hist + B;                   // [R+E]
-  const int n_items = kChunkTokens * J;
-  const int c = blockIdx.x;
-  const int t0 = c * kChunkTokens;
+constexpr int kNotifyWarps = 8;
 
-  for (int i = threadIdx.x; i < B; i += blockDim.x) hist[i] = 0;
-  for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
-    const int t = t0 + i / J, j = i % J;
-    int b = -1;
-    if (t < g.T) {
-      if (MODE == 0) {
-        b = is_in_rank[(size_t)t * R + j] ? j : -1;
-      } else {
-        const long long e = topk_idx[(size_t)t * g.K + j];
-        b = (e >= 0 && e < E) ? (int)e : -1;
+template <int MODE>
+__global__ void __launch_bounds__(kNotifyWarps * 32)
+notify_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, const bool* __restrict__ is_in_rank,
+                   const long long* __restrict__ topk_idx,
+                   const int* __restrict__ num_tokens_per_expert, int* __restrict__ item_rank,
+                   int* chunk_hist, unsigned int* block_counter, int* status) {
+  extern __shared__ int sh[];
+  const int J = g.J, B = g.B, R = g.R, E = g.E, K = g.K;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned lt = (1u << lane) - 1u;
+  const int C = g.T > 0 ? (g.T + kChunkTokens - 1) / kChunkTokens : 1;
+  const int c = blockIdx.x * kNotifyWarps + warp;
+  if (c < C) {
+    const int t = c * kChunkTokens + lane;
+    const bool valid = t < g.T;
+    if (MODE == 0) {
+      for (int j = 0; j < R; ++j) {
+        const bool in = valid && is_in_rank[(size_t)t * R + j];
+        const unsigned m = __ballot_sync(0xffffffffu, in);
+        if (valid) item_rank[(size_t)t * J + j] = in ? __popc(m & lt) : -1;
+        if (lane == 0) chunk_hist[(size_t)c * B + j] = __popc(m);
       }
+    } else {
+      unsigned int* bits = reinterpret_cast<unsigned int*>(sh) + (size_t)warp * B;
+      for (int b = lane; b < B; b += 32) bits[b] = 0u;
+      __syncwarp();
+      bool dup = false;
+      for (int k = 0; k < K; ++k) {
+        const long long e = valid ? topk_idx[(size_t)t * K + k] : -1;
+        if (e >= 0 && e < E) {
+          const unsigned old = atomicOr(&bits[(int)e], 1u << lane);
+          if (old & (1u << lane)) dup = true;     // the same expert twice in one token
+        } else if (e != -1) {
+          set_status(status, kBadExpertIndex);
+        }
+      }
+      if (dup) set_status(status, kBadExpertIndex);
+      __syncwarp();
+      for (int k = 0; k < K && valid; ++k) {
+        const long long e = topk_idx[(size_t)t * K + k];
+        int r = -1;
+        if (e >= 0 && e < E) {
+          r = __popc(bits[(int)e] & lt);
+          if (dup)                                 // keep the first occurrence only
+            for (int q = 0; q < k; ++q)
+              if (topk_idx[(size_t)t * K + q] == e) r = -1;
+        }
+        item_rank[(size_t)t * J + k] = r;
+      }
+      for (int b = lane; b < B; b += 32) chunk_hist[(size_t)c * B + b] = __popc(bits[b]);
     }
-    items[i] = b;
   }
-  __syncthreads();
-  for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
-    const int b = items[i];
-    int r = -1;
-    if (b >= 0) {
-      r = 0;
-      for (int q = 0; q < i; ++q) r += (items[q] == b);
-      atomicAdd(&hist[b], 1);
-    }
-    const int t = t0 + i / J;
-    if (t < g.T) item_rank[(size_t)t * J + i % J] = r;
-  }
-  __syncthreads();
-  for (int b = threadIdx.x; b < B; b += blockDim.x) chunk_hist[(size_t)c * B + b] = hist[b];
 
   if (!last_block_arrive(block_counter, gridDim.x)) return;
 
-  // ---- last block: exclusive scan over chunks, per bucket (one warp per bucket, 32 chunks per
-  // step, coalesced loads issued together; a serial loop here costs one L2 round trip per chunk) ----
-  const int C = gridDim.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int b = warp; b < B; b += nwarps) {
-    int carry = 0;
-    for (int c0 = 0; c0 < C; c0 += 32) {
-      const int cc = c0 + lane;
-      const int v = cc < C ? __ldcg(&chunk_hist[(size_t)cc * B + b]) : 0;
-      int incl = v;
+  // ---- last block: exclusive scan over chunks, per bucket -------------------------------
+  int* hist = sh + (MODE == 1 ? kNotifyWarps * B : 0);   // [B] totals
+  int* vec = hist + B;                                   // [R+E]
+  if (B <= kNotifyWarps * 2) {
+    // few buckets: one warp per bucket, lanes over chunks, all loads of a pass issued together
+    for (int b = warp; b < B; b += kNotifyWarps) {
+      int carry = 0;
+      for (int c0 = 0; c0 < C; c0 += 128) {
+        int v[4];
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int n = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += n;
+        for (int u = 0; u < 4; ++u) {
+          const int cc = c0 + u * 32 + lane;
+          v[u] = cc < C ? __ldcg(&chunk_hist[(size_t)cc * B + b]) : 0;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int cc = c0 + u * 32 + lane;
+          int incl = v[u];
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += n;
+          }
+          if (cc < C) chunk_hist[(size_t)cc * B + b] = carry + incl - v[u];
+          carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
       }
-      if (cc < C) chunk_hist[(size_t)cc * B + b] = carry + incl - v;
-      carry += __shfl_sync(0xffffffffu, incl, 31);
+      if (lane == 0) hist[b] = carry;
     }
-    if (lane == 0) hist[b] = carry;  // total per bucket
+  } else {
+    // many buckets: one thread per bucket (coalesced across buckets), chunks in batches of
+    // independent loads
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+      int carry = 0;
+      for (int c0 = 0; c0 < C; c0 += 16) {
+        int v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) v[u] = (c0 + u < C) ? __ldcg(&chunk_hist[(size_t)(c0 + u) * B + b]) : 0;
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          if (c0 + u < C) chunk_hist[(size_t)(c0 + u) * B + b] = carry;
+          carry += v[u];
+        }
+      }
+      hist[b] = carry;
+    }
   }
   __syncthreads();
   const int V = R + E;
@@ -170,109 +226,19 @@ void launch_notify_send(const EpGeom& g, const EpRegions& rg, const PeerPtrs& pe
                         const int* num_tokens_per_expert, int* item_rank, int* chunk_hist,
                         unsigned int* block_counter, int* status, cudaStream_t st) {
   const int C = g.T > 0 ? (g.T + kChunkTokens - 1) / kChunkTokens : 1;
-  int threads = kChunkTokens * g.J;
-  if (threads < 256) threads = 256;
-  if (threads > 1024) threads = 1024;
-  const size_t smem = sizeof(int) * (kChunkTokens * g.J + g.B + g.R + g.E);
-  if (g.mode == 0)
-    notify_send_kernel<0><<<C, threads, smem, st>>>(g, rg, peers, is_in_rank, topk_idx,
-                                                    num_tokens_per_expert, item_rank, chunk_hist,
-                                                    block_counter, status);
-  else
-    notify_send_kernel<1><<<C, threads, smem, st>>>(g, rg, peers, is_in_rank, topk_idx,
-                                                    num_tokens_per_expert, item_rank, chunk_hist,
-                                                    block_counter, status);
-}
-
-// ---------------------------------------------------------------------------------------
-// notify_wait: one CTA. Waits (bounded) for every peer's count vector, then derives
-//   send_base[b]  row in the destination where my stream for bucket b starts,
-//   comb_base[b]  slot in MY combine region where results for bucket b start,
-//   recv offsets / counts on my side, and publishes N_recv + per-expert counts to pinned
-//   host memory so the host can size the output tensors without a device synchronise.
-// ---------------------------------------------------------------------------------------
-__global__ void notify_wait_kernel(EpGeom g, EpRegions rg, char* self_base, EpMeta m,
-                                   volatile int* host_word, int* status) {
-  extern __shared__ int col[];  // [E] column totals
-  __shared__ int ok;
-  const int R = g.R, E = g.E, El = g.El, V = g.R + g.E, me = g.rank;
-  const int* flags = reinterpret_cast<const int*>(self_base + rg.flags) + kChNotify * kMaxRanks;
-  const int* M = reinterpret_cast<const int*>(self_base + rg.counts);
-  if (threadIdx.x == 0) ok = 1;
-  __syncthreads();
-  if (threadIdx.x < R) {
-    if (!wait_flag_ge(flags + threadIdx.x, g.epoch, g.timeout_ns, status, kTimeoutNotify)) ok = 0;
-  }
-  __syncthreads();
-  if (!ok) {
-    if (threadIdx.x == 0) {
-      *m.n_recv = 0;
-      *m.send_total = -1;      // tells dispatch_send that the offsets are not valid: send nothing
-      host_word[1] = -1;
-      __threadfence_system();
-      host_word[0] = g.epoch;
-    }
-    return;
-  }
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int s = 0;
-    for (int r = 0; r < R; ++r) s += __ldcg(&M[r * V + R + e]);
-    col[e] = s;
-  }
-  __syncthreads();
+  const int blocks = (C + kNotifyWarps - 1) / kNotifyWarps;
+  const size_t smem = sizeof(int) * ((g.mode == 1 ? kNotifyWarps * g.B : 0) + g.B + g.R + g.E);
   if (g.mode == 0) {
-    for (int d = threadIdx.x; d < R; d += blockDim.x) {
-      int sb = 0, cb = 0;
-      for (int s = 0; s < me; ++s) sb += __ldcg(&M[s * V + d]);
-      for (int q = 0; q < d; ++q) cb += __ldcg(&M[me * V + q]);
-      m.send_base[d] = sb;
-      m.comb_base[d] = cb;
-    }
+    notify_send_kernel<0><<<blocks, kNotifyWarps * 32, smem, st>>>(
+        g, rg, peers, is_in_rank, topk_idx, num_tokens_per_expert, item_rank, chunk_hist,
+        block_counter, status);
   } else {
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-      const int d = e / El, gl = e % El;
-      int sb = 0, cb = 0;
-      for (int q = 0; q < gl; ++q) sb += col[d * El + q];
-      for (int s = 0; s < me; ++s) sb += __ldcg(&M[s * V + R + e]);
-      for (int q = 0; q < e; ++q) cb += __ldcg(&M[me * V + R + q]);
-      m.send_base[e] = sb;
-      m.comb_base[e] = cb;
-    }
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(notify_send_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    notify_send_kernel<1><<<blocks, kNotifyWarps * 32, smem, st>>>(
+        g, rg, peers, is_in_rank, topk_idx, num_tokens_per_expert, item_rank, chunk_hist,
+        block_counter, status);
   }
-  if (threadIdx.x == 0) {
-    int n_recv = 0, acc = 0, stot = 0;
-    for (int s = 0; s < R; ++s) {
-      m.recv_src_off[s] = n_recv;
-      n_recv += __ldcg(&M[s * V + me]);
-    }
-    m.recv_src_off[R] = n_recv;
-    for (int q = 0; q < El; ++q) {
-      const int cnt = col[me * El + q];
-      m.recv_expert_cnt[q] = cnt;
-      m.recv_expert_off[q] = acc;
-      acc += cnt;
-      host_word[2 + q] = cnt;
-    }
-    m.recv_expert_off[El] = acc;
-    if (g.mode == 1) {
-      n_recv = acc;
-      for (int q = 0; q < E; ++q) stot += __ldcg(&M[me * V + R + q]);
-    } else {
-      for (int q = 0; q < R; ++q) stot += __ldcg(&M[me * V + q]);
-    }
-    *m.n_recv = n_recv;
-    *m.send_total = stot;
-    if (n_recv > g.cap) set_status(status, kOverflowRecv);
-    if (stot > g.slot_cap) set_status(status, kOverflowSlots);
-    host_word[1] = n_recv;
-    __threadfence_system();
-    host_word[0] = g.epoch;
-  }
-}
-
-void launch_notify_wait(const EpGeom& g, const EpRegions& rg, char* self_base, const EpMeta& m,
-                        int* host_word, int* status, cudaStream_t st) {
-  notify_wait_kernel<<<1, 256, sizeof(int) * g.E, st>>>(g, rg, self_base, m, host_word, status);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -25,7 +25,10 @@ constexpr int kLLThreads = 256;  // 8 warps work on one row together
 // Send half: works with epoch = [0]+1, target = [1]+grid; CTA 0 publishes them in [2],[3].
 // Receive half (next launch on the stream): reads [2],[3]; CTA 0 commits them to [0],[1].
 // No kernel ever reads a word that another CTA of the same launch writes.
-struct LLTick { int epoch, target; };
+// The arrival target is a cumulative count modulo 2^32 (it grows by the grid size per call and
+// passes 2^31 after a few hours of decode steps): it is advanced in unsigned arithmetic and compared
+// with `counter_reached`, never with a signed `>=`. Epochs grow by 1 per call and stay signed.
+struct LLTick { int epoch; unsigned int target; };
 
 // First statement of every kernel below. When a kernel is launched with programmatic stream
 // serialisation (P.pdl), its CTAs may be placed on the SMs while the previous kernel of the stream
@@ -41,11 +44,11 @@ __device__ __forceinline__ LLTick ll_tick_send(int* st, int grid_ctas) {
   __shared__ int s_e, s_t;
   if (threadIdx.x == 0) {
     s_e = *reinterpret_cast<volatile int*>(st + 0) + 1;
-    s_t = *reinterpret_cast<volatile int*>(st + 1) + grid_ctas;
+    s_t = (int)((unsigned int)*reinterpret_cast<volatile int*>(st + 1) + (unsigned int)grid_ctas);
     if (blockIdx.x == 0 && blockIdx.y == 0) { st[2] = s_e; st[3] = s_t; }
   }
   __syncthreads();
-  return LLTick{s_e, s_t};
+  return LLTick{s_e, (unsigned int)s_t};
 }
 __device__ __forceinline__ LLTick ll_tick_recv(int* st) {
   __shared__ int s_e, s_t;
@@ -55,7 +58,7 @@ __device__ __forceinline__ LLTick ll_tick_recv(int* st) {
     if (blockIdx.x == 0 && blockIdx.y == 0) { st[0] = s_e; st[1] = s_t; }
   }
   __syncthreads();
-  return LLTick{s_e, s_t};
+  return LLTick{s_e, (unsigned int)s_t};
 }
 // Every CTA of a send kernel ends with this. A receiver waits for this rank's arrival counter
 // (one per peer and channel, cumulative) to reach the target, i.e. for ALL CTAs of the sender
@@ -202,7 +205,7 @@ ll_dispatch_recv_kernel(LLParams P, char* self_base, char* __restrict__ out_x,
   __syncthreads();
   if (threadIdx.x < P.R) {
     const int* flags = reinterpret_cast<const int*>(self_base + P.flags) + kChLLDispatch * kMaxRanks;
-    if (!wait_flag_ge(flags + threadIdx.x, tk.target, P.timeout_ns, status, kTimeoutLowLatency)) ok = 0;
+    if (!wait_counter_reached(flags + threadIdx.x, tk.target, P.timeout_ns, status, kTimeoutLowLatency)) ok = 0;
   }
   __syncthreads();
   const int el = blockIdx.x;
@@ -320,7 +323,7 @@ ll_combine_recv_kernel(LLParams P, char* self_base, const long long* __restrict_
   __syncthreads();
   if (threadIdx.x < P.R) {
     const int* flags = reinterpret_cast<const int*>(self_base + P.flags) + kChLLCombine * kMaxRanks;
-    if (!wait_flag_ge(flags + threadIdx.x, tk.target, P.timeout_ns, status, kTimeoutLowLatency)) ok = 0;
+    if (!wait_counter_reached(flags + threadIdx.x, tk.target, P.timeout_ns, status, kTimeoutLowLatency)) ok = 0;
   }
   __syncthreads();
   if (!ok) return;

@@ -64,13 +64,18 @@ class DispatchHandle:
     n_recv: int
     send_row: torch.Tensor         # [T,J] int32 row at the destination (-1 = not sent)
     send_slot: torch.Tensor        # [T,J] int32 slot in my combine region (-1 = none)
-    meta: torch.Tensor             # int32 device metadata (counts, prefixes)
+    meta: torch.Tensor             # int32 device metadata (counts, prefixes, chunk boundaries)
     recv_meta: torch.Tensor        # [n_recv,2] int32 {slot at source, source rank}
     topk_idx: Optional[torch.Tensor]
     is_token_in_rank: Optional[torch.Tensor]
     num_recv_tokens_per_expert_list: List[int] = field(default_factory=list)
     fp8: bool = False
     recv_prob: Optional[torch.Tensor] = None
+    bnd: Optional[torch.Tensor] = None     # [R, BND_STRIDE] first receive row of (source, token chunk); rank mode
+    nch: int = 0                           # combine chunks per rank used by this dispatch
+    chunk_tokens: int = 32                 # tokens per combine chunk on THIS rank
+    carve_key: tuple = ()                  # region layout that the rows / slots refer to
+    cap: int = 0                           # receive capacity (rows) of that layout
 
     @property
     def n_recv_dev(self) -> torch.Tensor:
@@ -78,13 +83,23 @@ class DispatchHandle:
 
 
 class _Carve:
-    """Byte offsets of every region for one (E, K, H, row bytes, combine row bytes) shape."""
+    """Byte offsets of every region for one (E, K, H, row bytes, combine row bytes) shape.
 
-    def __init__(self, nbytes: int, R: int, E: int, K: int, H: int, row_bytes: int, comb_row_bytes: int):
+    The control area starts with the blocks whose position must never depend on the shape (flag
+    words are epochs that only grow, so a word must not be reused for anything else): channel
+    flags, per-chunk combine flags, chunk-boundary tables. The count matrices follow."""
+
+    def __init__(self, nbytes: int, R: int, E: int, K: int, H: int, row_bytes: int, comb_row_bytes: int,
+                 max_recv_rows: int = 0):
         C = _ext.load()
         self.key = (E, K, H, row_bytes, comb_row_bytes)
         self.flags = 0
         off = align_up(C.NUM_CHANNELS * C.MAX_RANKS * 4, REGION_ALIGN)
+        self.chunk_flags = off
+        off = align_up(off + C.MAX_RANKS * C.MAX_COMB_CHUNKS * 4, REGION_ALIGN)
+        bsz = align_up(C.MAX_RANKS * C.BND_STRIDE * 4, REGION_ALIGN)
+        self.recv_bnd = (off, off + bsz)
+        off += 2 * bsz
         csz = align_up(R * (R + E) * 4, REGION_ALIGN)
         self.counts = (off, off + csz)
         off += 2 * csz
@@ -97,6 +112,8 @@ class _Carve:
         per_row = sum(sizes.values())
         avail = nbytes - FIXED_BYTES - 2 * len(sizes) * REGION_ALIGN
         self.cap = max(avail // (2 * per_row), 0)
+        if max_recv_rows > 0:
+            self.cap = min(self.cap, int(max_recv_rows))
         self.slot_cap = self.cap
         self.regions = []  # per parity: dict name -> offset
         off = FIXED_BYTES
@@ -107,15 +124,23 @@ class _Carve:
                 off = align_up(off + self.cap * sz, REGION_ALIGN)
             self.regions.append(d)
         assert off <= nbytes or self.cap == 0
+        self.bytes_used = off
+        self._lists = {}
 
     def region_list(self, notify_parity: int, dispatch_parity: int, combine_parity: int):
-        d, c = self.regions[dispatch_parity], self.regions[combine_parity]
-        return [self.flags, self.counts[notify_parity], d["recv_x"], d["recv_scales"],
-                d["recv_topk_idx"], d["recv_topk_w"], d["recv_meta"], d["recv_prob"],
-                c["comb_x"], c["comb_w"]]
+        key = (notify_parity, dispatch_parity, combine_parity)
+        out = self._lists.get(key)
+        if out is None:
+            d, c = self.regions[dispatch_parity], self.regions[combine_parity]
+            out = [self.flags, self.counts[notify_parity], d["recv_x"], d["recv_scales"],
+                   d["recv_topk_idx"], d["recv_topk_w"], d["recv_meta"], d["recv_prob"],
+                   c["comb_x"], c["comb_w"], self.chunk_flags, self.recv_bnd[dispatch_parity]]
+            self._lists[key] = out
+        return out
 
 
 _ELEM_DTYPE = {torch.bfloat16: "bfloat16", torch.float16: "float16", torch.float32: "float32"}
+_STATUS_MIRROR_SLOT = 4000     # int index inside the mapped host block that mirrors the status word
 
 
 def _nvtx(name):
@@ -137,6 +162,9 @@ def _nvtx(name):
 
 class Buffer:
     num_sms: int = 24
+    # Combine chunks per rank (0 = one flag per rank when the whole send is done). Must be the same
+    # on every rank of the group. The source reduces chunk c while chunk c+1 is still arriving.
+    combine_chunks: int = 16
 
     # ---- static configuration --------------------------------------------------------
     @staticmethod
@@ -147,20 +175,23 @@ class Buffer:
 
     @staticmethod
     def get_dispatch_config(group_size: int, num_max_tokens_per_rank: int = 4096, num_topk: int = 8,
-                            num_experts: int = 256, group_by_expert: bool = False) -> Config:
+                            num_experts: int = 256, group_by_expert: bool = False,
+                            num_max_recv_tokens: int = 0) -> Config:
         return Config(Buffer.num_sms, num_max_tokens_per_rank, num_topk, num_experts,
-                      group_by_expert=group_by_expert)
+                      group_by_expert=group_by_expert, num_max_recv_tokens=num_max_recv_tokens)
 
     @staticmethod
     def get_combine_config(group_size: int, num_max_tokens_per_rank: int = 4096, num_topk: int = 8,
-                           num_experts: int = 256, group_by_expert: bool = False) -> Config:
+                           num_experts: int = 256, group_by_expert: bool = False,
+                           num_max_recv_tokens: int = 0) -> Config:
         return Config(Buffer.num_sms, num_max_tokens_per_rank, num_topk, num_experts,
-                      group_by_expert=group_by_expert)
+                      group_by_expert=group_by_expert, num_max_recv_tokens=num_max_recv_tokens)
 
     # ---- construction ----------------------------------------------------------------
     def __init__(self, group=None, num_nvl_bytes: int = 0, num_rdma_bytes: int = 0,
                  low_latency_mode: bool = False, num_qps_per_rank: int = 1, *,
-                 world=None, timeout_s: float = 20.0, blocks_per_sm: int = 2):
+                 world=None, timeout_s: float = 20.0, blocks_per_sm: int = 2,
+                 num_max_recv_tokens: int = 0):
         self.C = _ext.load()
         self.world = world if world is not None else ProcessWorld(group)
         self.group = group
@@ -173,18 +204,26 @@ class Buffer:
         self.device = self.world.device
         self.timeout_s = float(timeout_s)
         self.blocks_per_sm = blocks_per_sm
+        self.num_max_recv_tokens = int(num_max_recv_tokens)
         if self.num_nvl_bytes < FIXED_BYTES + REGION_ALIGN:
             raise ValueError("num_nvl_bytes too small; use Config.get_nvl_buffer_size_hint")
         self.region = SymmetricRegion(self.world, self.num_nvl_bytes)
+        self.host_word = self.C.host_mapped_alloc(4 * 4096)
         with torch.cuda.device(self.device):
+            # status block: [0] first fault code, [2..3] address of the host word that mirrors it
             self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+            self.status.view(torch.int64)[1] = self.host_word + 4 * _STATUS_MIRROR_SLOT
             self.counters = torch.zeros(8, dtype=torch.int32, device=self.device)
+            self._comb_scratch = torch.zeros(self.C.MAX_RANKS * self.C.MAX_COMB_CHUNKS + 2,
+                                             dtype=torch.int32, device=self.device)
             self._side_stream = (torch.cuda.current_stream() if self.world.local
                                  else torch.cuda.Stream(device=self.device))
             self.comm_stream = torch.cuda.current_stream()
         self._async_outstanding = False
+        # One launch may both send and wait for peers only when no other rank shares this GPU.
+        self._single_launch = (not self.world.local) or self.group_size == 1
         self._ws = {}
-        self.host_word = self.C.host_mapped_alloc(4 * 4096)
+        self._layout_ws = None
         self._epoch = dict(notify=0, dispatch=0, combine=0, barrier=0, ll_dispatch=0, ll_combine=0)
         self._carve: Optional[_Carve] = None
         self._ll = None
@@ -203,11 +242,16 @@ class Buffer:
     # ---- helpers ---------------------------------------------------------------------
     @property
     def peers(self) -> List[int]:
-        return list(self.region.peer_ptrs)
+        return self.region.peer_ptrs
 
     @property
     def status_ptr(self) -> int:
         return self.status.data_ptr()
+
+    @property
+    def bytes_reserved(self) -> int:
+        """Bytes of the symmetric region that the current shape actually uses (both parities)."""
+        return self._carve.bytes_used if self._carve is not None else FIXED_BYTES
 
     def _timeout_ns(self) -> int:
         return int(self.timeout_s * 1e9)
@@ -215,13 +259,33 @@ class Buffer:
     def _blocks(self) -> int:
         return max(1, Buffer.num_sms * self.blocks_per_sm)
 
+    def _clear_status(self) -> None:
+        self.status[0:2].zero_()
+        self.counters.zero_()
+        self._comb_scratch.zero_()
+        self.C.host_write_i32(self.host_word, _STATUS_MIRROR_SLOT, 0)
+
+    @staticmethod
+    def _raise_status(code: int):
+        cls = EpTimeoutError if code in (1, 2, 3, 4, 5, 8, 9) else EpStatusError
+        raise cls(f"b200ep status {code}: {STATUS_TEXT.get(code, 'unknown')}")
+
     def check_status(self) -> None:
         """Synchronising read of the device status word; raises on any recorded fault."""
         code = int(self.status[0].item())
         if code != 0:
-            self.status.zero_()
-            cls = EpTimeoutError if code in (1, 2, 3, 4, 5, 8, 9) else EpStatusError
-            raise cls(f"b200ep status {code}: {STATUS_TEXT.get(code, 'unknown')}")
+            self._clear_status()
+            self._raise_status(code)
+
+    def _poll_status(self) -> None:
+        """Non-synchronising check: a kernel that records a fault also copies the code to a mapped
+        host word. Called on entry to every public op, so a time-out or overflow of an EARLIER op
+        surfaces as an exception at the next call instead of as silently incomplete tensors."""
+        code = self.C.host_read_i32(self.host_word, _STATUS_MIRROR_SLOT)
+        if code != 0:
+            torch.cuda.synchronize(self.device)
+            self._clear_status()
+            self._raise_status(code)
 
     def _get_carve(self, E: int, K: int, H: int, row_bytes: int, comb_row_bytes: int) -> _Carve:
         key = (E, K, H, row_bytes, comb_row_bytes)
@@ -229,13 +293,31 @@ class Buffer:
             if self._carve is not None or self._ll is not None:
                 self.barrier()           # region reuse with another shape: drain every rank first
             self._ll = None
-            self._carve = _Carve(self.num_nvl_bytes, self.group_size, E, K, H, row_bytes, comb_row_bytes)
+            self._carve = _Carve(self.num_nvl_bytes, self.group_size, E, K, H, row_bytes, comb_row_bytes,
+                                 self.num_max_recv_tokens)
         return self._carve
 
-    def _geom(self, *, E, K, T, mode, H, cap, slot_cap, epoch) -> List[int]:
+    def _chunks(self, T: int):
+        """(nch, tokens per chunk) of this rank's combine chunks: nch is the same on every rank,
+        the chunk length depends on this rank's token count (a multiple of 32)."""
+        nch = max(0, min(int(Buffer.combine_chunks), self.C.MAX_COMB_CHUNKS))
+        if nch == 0:
+            return 0, self.C.CHUNK_TOKENS
+        c32 = max((T + self.C.CHUNK_TOKENS - 1) // self.C.CHUNK_TOKENS, 1)
+        return nch, ((c32 + nch - 1) // nch) * self.C.CHUNK_TOKENS
+
+    def _geom(self, *, E, K, T, mode, H, cap, slot_cap, epoch, epoch_wait=0, nch=0, chunk_tokens=32,
+              tail_wait=0) -> List[int]:
         R = self.group_size
         J, B = (R, R) if mode == 0 else (K, E)
-        return [self.rank, R, E, E // R, K, T, mode, J, B, H, cap, slot_cap, epoch, self._timeout_ns()]
+        return [self.rank, R, E, E // R, K, T, mode, J, B, H, cap, slot_cap, epoch, epoch_wait, nch,
+                chunk_tokens, tail_wait, self._timeout_ns()]
+
+    def _meta_ints(self, E: int, mode: int, K: int) -> int:
+        R = self.group_size
+        El = E // R
+        B = R if mode == 0 else E
+        return 2 + El + (El + 1) + (R + 1) + 2 * B + R * self.C.BND_STRIDE
 
     def _enter(self, previous_event, allocate_on_comm_stream, async_finish):
         """Pick the stream for this op. Synchronous calls run on the caller's stream (no stream
@@ -243,6 +325,7 @@ class Buffer:
         buffer's own communication stream."""
         if allocate_on_comm_stream and not async_finish:
             raise ValueError("allocate_on_comm_stream=True requires async_finish=True")
+        self._poll_status()
         compute = torch.cuda.current_stream(self.device)
         use_side = (async_finish or previous_event is not None) and not self.world.local
         if not use_side:
@@ -279,15 +362,18 @@ class Buffer:
             self.C.barrier(self.peers, 0, self.rank, self.group_size, self._epoch["barrier"],
                            self._timeout_ns(), self.status_ptr, not self.world.local)
 
-    def probe_timeout(self, timeout_s: float = 0.2) -> int:
+    def probe_timeout(self, timeout_s: float = 0.2, clear: bool = True) -> int:
         """Wait on a flag that nothing sets, with a short limit; returns the status code that the
-        kernel recorded (8) and clears it. Shows that a lost peer ends in an error, not a hang."""
+        kernel recorded (8). Shows that a lost peer ends in an error, not a hang. With
+        `clear=False` the fault is left recorded, as after a real time-out: the next public op on
+        this buffer raises it."""
         self._enter(None, False, False)
         with torch.cuda.stream(self.comm_stream):
             self.C.wait_flags(self.region.local_ptr, 0, self.C.NUM_CHANNELS - 1, 1, 1 << 30,
                               int(timeout_s * 1e9), self.status_ptr, 8)
         code = int(self.status[0].item())
-        self.status.zero_()
+        if clear:
+            self._clear_status()
         return code
 
     # ---- layout ----------------------------------------------------------------------
@@ -306,10 +392,14 @@ class Buffer:
         compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
         with torch.cuda.stream(self.comm_stream):
             T = topk_idx.shape[0]
+            need = self.C.layout_scratch_ints(T, num_experts, R)
+            if self._layout_ws is None or self._layout_ws.numel() < need:
+                self._layout_ws = torch.empty(need, dtype=torch.int32, device=self.device)
             counts = torch.empty(R + num_experts, dtype=torch.int32, device=self.device)
             per_rank, per_expert = counts[:R], counts[R:]
             in_rank = torch.empty((T, R), dtype=torch.bool, device=self.device)
-            self.C.layout(topk_idx, num_experts, R, per_rank, per_expert, in_rank, self.status_ptr)
+            self.C.layout(topk_idx, num_experts, R, per_rank, per_expert, in_rank, self._layout_ws,
+                          self.counters[4:5], self.status_ptr)
         ev = self._exit(compute, async_finish, (per_rank, per_expert, in_rank, topk_idx))
         return per_rank, None, per_expert, in_rank, ev
 
@@ -370,11 +460,19 @@ class Buffer:
         J, B = (R, R) if mode == 0 else (K, E)
         st.update(J=J, B=B, row_bytes_out=row_bytes_out)
         if st["cached"]:
+            # the handle's rows and slots index the region layout of ITS dispatch
+            if handle.carve_key != carve.key or handle.cap > carve.cap:
+                raise ValueError("cached dispatch: the handle was made for another region layout "
+                                 f"(row bytes / capacity {handle.carve_key}, {handle.cap}) than this "
+                                 f"input would use ({carve.key}, {carve.cap}); dispatch the same element "
+                                 "width as the handle's own dispatch")
             st["meta"] = handle.meta
             st["send_row"], st["send_slot"] = handle.send_row, handle.send_slot
+            st["nch"], st["chunk_tokens"] = handle.nch, handle.chunk_tokens
             return st
         self._epoch["notify"] += 1
         st["epoch_n"] = self._epoch["notify"]
+        st["nch"], st["chunk_tokens"] = self._chunks(T)
         dev = self.device
         C_chunks = max((T + self.C.CHUNK_TOKENS - 1) // self.C.CHUNK_TOKENS, 1)
         key = (max(T, 1), J, C_chunks, B)
@@ -384,8 +482,7 @@ class Buffer:
                   torch.empty((C_chunks, B), dtype=torch.int32, device=dev))
             self._ws = {key: ws}
         st["item_rank"], st["chunk_hist"] = ws
-        El = E // R
-        n_meta = 2 + El + (El + 1) + (R + 1) + 2 * B
+        n_meta = self._meta_ints(E, mode, K)
         n_tj = max(T, 1) * J
         owned = torch.empty(n_meta + 2 * n_tj, dtype=torch.int32, device=dev)   # handle-owned ints
         st["meta"] = owned[:n_meta]
@@ -405,6 +502,9 @@ class Buffer:
         return st
 
     def _dispatch_p2(self, st):
+        """The send kernel. One process per GPU: its last CTA also waits for the peers, so the
+        receive region is complete when the kernel ends. Virtual ranks on one GPU: the wait is a
+        separate launch (`_dispatch_p3`) issued after every rank's send."""
         carve = st["carve"]
         self._epoch["dispatch"] += 1
         st["epoch_d"] = self._epoch["dispatch"]
@@ -412,20 +512,23 @@ class Buffer:
         regions = carve.region_list(pn, st["epoch_d"] & 1, 0)
         st["regions"] = regions
         geom = self._geom(E=st["E"], K=st["K"], T=st["T"], mode=st["mode"], H=st["H"], cap=carve.cap,
-                          slot_cap=carve.slot_cap, epoch=st.get("epoch_n", 0))
-        if not st["cached"]:
-            self.C.notify_wait(geom, regions, self.region.local_ptr, st["meta"], self.host_word,
-                               self.status_ptr)
-        geom[12] = st["epoch_d"]
+                          slot_cap=carve.slot_cap, epoch=st["epoch_d"], epoch_wait=st.get("epoch_n", 0),
+                          nch=st["nch"], chunk_tokens=st["chunk_tokens"],
+                          tail_wait=1 if self._single_launch else 0)
+        st["geom"] = geom
         self.C.dispatch_send(geom, regions, self.peers, st["meta"], st["x"], st["fp8"], st["cached"],
                              st["topk_idx"], st.get("topk_weights"), st.get("item_rank"),
                              st.get("chunk_hist"), st["send_row"], st["send_slot"],
-                             self.counters[1:2], self.status_ptr, self._blocks(), st.get("scales_in"))
+                             self.counters[1:2], self.host_word, self.status_ptr, self._blocks(),
+                             st.get("scales_in"))
 
-    def _dispatch_p3(self, st, zero_copy: bool, num_worst_tokens: int = 0):
+    def _dispatch_p3(self, st, zero_copy: bool, num_worst_tokens: int = 0, expert_alignment: int = 1):
         R, E, K, H = self.group_size, st["E"], st["K"], st["H"]
         El = E // R
         carve = st["carve"]
+        if not self._single_launch:
+            self.C.dispatch_wait(st["geom"], st["regions"], self.region.local_ptr, st["meta"], st["cached"],
+                                 self.status_ptr)
         if st["cached"]:
             h = st["handle"]
             n_recv, per_expert_list = h.n_recv, h.num_recv_tokens_per_expert_list
@@ -440,13 +543,17 @@ class Buffer:
                 raise EpTimeoutError("host timed out waiting for the receive count")
             n_recv = self.C.host_read_i32(self.host_word, 1)
             if n_recv < 0:
-                self.status.zero_()
+                torch.cuda.synchronize(self.device)
+                self._clear_status()
                 raise EpTimeoutError("b200ep status 1: " + STATUS_TEXT[1])
             if n_recv > carve.cap:
+                torch.cuda.synchronize(self.device)
+                self._clear_status()
                 raise EpStatusError(f"receive region overflow: {n_recv} rows > capacity {carve.cap}")
             per_expert_list = self.C.host_read_i32_list(self.host_word, 2, El)
-        self.C.wait_flags(self.region.local_ptr, 0, 1, R, st["epoch_d"], self._timeout_ns(),
-                          self.status_ptr, 2)
+            if expert_alignment > 1:
+                per_expert_list = [align_up(c, expert_alignment) for c in per_expert_list]
+            self._poll_status()       # the host already waited for the kernel's prologue: cheap to look
         reg = dict(zip(("flags", "counts", "recv_x", "recv_scales", "recv_topk_idx", "recv_topk_w",
                         "recv_meta", "recv_prob", "comb_x", "comb_w"), st["regions"]))
         keep = (lambda t: t) if zero_copy else (lambda t: t.clone())
@@ -460,14 +567,19 @@ class Buffer:
             return recv_x, None, None, per_expert_list, st["handle"]
         recv_topk_idx = recv_topk_w = recv_prob = None
         if st["mode"] == 0 and st["topk_idx"] is not None:
-            recv_topk_idx = self.region.view(reg["recv_topk_idx"], (n_recv, K), "int64").clone()
-            recv_topk_w = self.region.view(reg["recv_topk_w"], (n_recv, K), "float32").clone()
+            recv_topk_idx = keep(self.region.view(reg["recv_topk_idx"], (n_recv, K), "int64"))
+            recv_topk_w = keep(self.region.view(reg["recv_topk_w"], (n_recv, K), "float32"))
         if st["mode"] == 1:
-            recv_prob = self.region.view(reg["recv_prob"], (n_recv,), "float32").clone()
-        recv_meta = self.region.view(reg["recv_meta"], (n_recv, 2), "int32").clone()
+            recv_prob = keep(self.region.view(reg["recv_prob"], (n_recv,), "float32"))
+        recv_meta = keep(self.region.view(reg["recv_meta"], (n_recv, 2), "int32"))
+        n_meta = st["meta"].numel()
+        bnd = None
+        if st["mode"] == 0 and st["nch"] > 0:
+            bnd = st["meta"][n_meta - R * self.C.BND_STRIDE:].view(R, self.C.BND_STRIDE)
         handle = DispatchHandle(st["mode"], st["T"], H, K, E, n_recv, st["send_row"], st["send_slot"],
                                 st["meta"], recv_meta, st["topk_idx"], st.get("is_token_in_rank"),
-                                per_expert_list, st["fp8_out"], recv_prob)
+                                per_expert_list, st["fp8_out"], recv_prob, bnd, st["nch"], st["chunk_tokens"],
+                                carve.key, carve.cap)
         return recv_x, recv_topk_idx, recv_topk_w, per_expert_list, handle
 
     @_nvtx("b200ep.dispatch")
@@ -484,16 +596,21 @@ class Buffer:
         then token; `recv_topk_idx` holds LOCAL expert ids, -1 where the expert lives elsewhere.
         `group_by_expert=True`: one row per (token, expert), rows grouped by local expert;
         the per-row router probability is in `handle.recv_prob`.
-        `zero_copy=True` returns views into the symmetric region that stay valid until the second
-        next dispatch on this buffer. `num_worst_tokens > 0` removes the host read of the receive
+        `zero_copy=True` returns views into the symmetric region (rows, routing side arrays and the
+        handle's row table alike) that stay valid until the second next dispatch on this buffer.
+        `num_worst_tokens > 0` removes the host read of the receive
         count: outputs have exactly that many rows (a bound chosen by the caller, e.g. group_size x
-        tokens per rank), the per-expert list is empty and the true count is `handle.n_recv_dev`."""
+        tokens per rank), the per-expert list is empty and the true count is `handle.n_recv_dev`.
+        `expert_alignment > 1` rounds every entry of the returned per-expert count list up to a
+        multiple of it (the rows themselves are not padded)."""
+        if expert_alignment < 1:
+            raise ValueError("expert_alignment must be >= 1")
         compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
         with torch.cuda.stream(self.comm_stream):
             st = self._dispatch_p1(x, handle, is_token_in_rank, num_tokens_per_expert, topk_idx,
                                    topk_weights, use_fp8, group_by_expert, num_experts)
             self._dispatch_p2(st)
-            out = self._dispatch_p3(st, zero_copy, num_worst_tokens)
+            out = self._dispatch_p3(st, zero_copy, num_worst_tokens, expert_alignment)
         flat = []
         for o in out[:3]:
             flat.extend(o if isinstance(o, tuple) else (o,))
@@ -501,7 +618,7 @@ class Buffer:
         return (*out, ev)
 
     # ---- combine ---------------------------------------------------------------------
-    def _combine_p1(self, x, handle: DispatchHandle, topk_weights):
+    def _combine_prepare(self, x, handle: DispatchHandle, topk_weights):
         if x.dim() != 2 or not x.is_contiguous() or x.shape[1] != handle.H:
             raise ValueError("x must be a contiguous [num_recv_tokens, hidden] tensor")
         if x.shape[0] < handle.n_recv:
@@ -516,20 +633,48 @@ class Buffer:
         self._epoch["combine"] += 1
         ep = self._epoch["combine"]
         regions = carve.region_list(0, 0, ep & 1)
+        by_chunk = handle.bnd is not None and handle.nch > 0
         geom = self._geom(E=handle.E, K=handle.K, T=handle.T, mode=handle.mode, H=handle.H,
-                          cap=handle.n_recv, slot_cap=carve.slot_cap, epoch=ep)
+                          cap=handle.n_recv, slot_cap=carve.slot_cap, epoch=ep,
+                          nch=handle.nch if by_chunk else 0, chunk_tokens=handle.chunk_tokens)
         if topk_weights is not None:
             topk_weights = topk_weights.to(torch.float32).contiguous()
-        self.C.combine_send(geom, regions, self.peers, handle.n_recv_dev, handle.recv_meta, x,
-                            topk_weights, self.counters[2:3], self.status_ptr, self._blocks())
-        return dict(ep=ep, regions=regions, geom=geom, dtype=x.dtype, with_w=topk_weights is not None)
+        return dict(ep=ep, regions=regions, geom=geom, dtype=x.dtype, topk_w=topk_weights, x=x,
+                    wait_mode=2 if by_chunk else 1)
 
-    def _combine_p2(self, st, handle: DispatchHandle, weights=None):
+    def _combine_outputs(self, st, handle: DispatchHandle):
         out = torch.empty((handle.T, handle.H), dtype=st["dtype"], device=self.device)
         out_w = (torch.empty((handle.T, handle.K), dtype=torch.float32, device=self.device)
-                 if st["with_w"] else None)
-        self.C.combine_reduce(st["geom"], st["regions"], self.region.local_ptr, handle.send_slot,
-                              weights, out, out_w, st["ep"], self.status_ptr, self._blocks() * 2)
+                 if st.get("topk_w") is not None else None)
+        return out, out_w
+
+    def _combine_p1(self, x, handle: DispatchHandle, topk_weights):
+        """Send half as its own launch (several virtual ranks on one GPU)."""
+        st = self._combine_prepare(x, handle, topk_weights)
+        self.C.combine(st["geom"], st["regions"], self.peers, 1, 0, self._blocks(), 0,
+                       handle.n_recv_dev, handle.recv_meta, x, st["topk_w"],
+                       handle.bnd if st["wait_mode"] == 2 else None, self._comb_scratch,
+                       None, None, None, None, self.status_ptr)
+        return st
+
+    def _combine_p2(self, st, handle: DispatchHandle, weights=None):
+        """Reduce half as its own launch."""
+        out, out_w = self._combine_outputs(st, handle)
+        self.C.combine(st["geom"], st["regions"], self.peers, 2, 0, self._blocks() * 2, st["wait_mode"],
+                       None, None, None, None, None, self._comb_scratch,
+                       handle.send_slot, weights, out, out_w, self.status_ptr)
+        return out, out_w
+
+    def _combine_fused(self, x, handle: DispatchHandle, topk_weights, weights=None):
+        """Both halves in ONE launch: the first `n_send` CTAs to start send, the others reduce each
+        token chunk as soon as every rank has returned it."""
+        st = self._combine_prepare(x, handle, topk_weights)
+        out, out_w = self._combine_outputs(st, handle)
+        n_send = max(1, Buffer.num_sms)
+        self.C.combine(st["geom"], st["regions"], self.peers, 0, n_send, 2 * n_send, st["wait_mode"],
+                       handle.n_recv_dev, handle.recv_meta, x, st["topk_w"],
+                       handle.bnd if st["wait_mode"] == 2 else None, self._comb_scratch,
+                       handle.send_slot, weights, out, out_w, self.status_ptr)
         return out, out_w
 
     @_nvtx("b200ep.combine")
@@ -547,8 +692,11 @@ class Buffer:
         weighted reduction applied on arrival."""
         compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
         with torch.cuda.stream(self.comm_stream):
-            st = self._combine_p1(x, handle, topk_weights)
-            out, out_w = self._combine_p2(st, handle, item_weights)
+            if self._single_launch:
+                out, out_w = self._combine_fused(x, handle, topk_weights, item_weights)
+            else:
+                st = self._combine_p1(x, handle, topk_weights)
+                out, out_w = self._combine_p2(st, handle, item_weights)
             if bias is not None:
                 out = out + (bias[0] if isinstance(bias, (tuple, list)) else bias)
         ev = self._exit(compute, async_finish, [out, x] + ([out_w] if out_w is not None else []))
@@ -771,7 +919,8 @@ def _fused_fc2_combine(self: Buffer, act: torch.Tensor, w2: torch.Tensor, handle
                                status_ptr=self.status_ptr)
         geom = self._geom(E=handle.E, K=handle.K, T=handle.T, mode=1, H=handle.H, cap=handle.n_recv,
                           slot_cap=carve.slot_cap, epoch=ep)
-        st = dict(ep=ep, regions=regions, geom=geom, dtype=torch.bfloat16, with_w=False)
+        # the GEMM's last CTA raises one flag per rank: the reduce launch waits for those
+        st = dict(ep=ep, regions=regions, geom=geom, dtype=torch.bfloat16, topk_w=None, wait_mode=1)
         out, _ = self._combine_p2(st, handle, item_weights)
     self._exit(compute, False, [out, act])
     return out

@@ -25,6 +25,10 @@ class Config:
     num_experts: int = 256
     combine_elem_bytes: int = 2
     group_by_expert: bool = False   # size for one row per (token, expert) instead of per (token, rank)
+    # Optional bound on the rows one rank can RECEIVE per dispatch (0 = worst case: every token of
+    # every rank lands here). A routing that exceeds the bound ends in status 6 (receive overflow),
+    # never in an out-of-range store. Pass the same value to `Buffer(num_max_recv_tokens=...)`.
+    num_max_recv_tokens: int = 0
 
     def per_row_bytes(self, hidden_bytes: int) -> int:
         """Bytes that one receive row plus one combine slot occupy (all side arrays)."""
@@ -40,6 +44,8 @@ class Config:
         if self.group_by_expert:
             # worst case: every token of every rank picks min(top-k, local experts) experts here
             rows *= max(1, min(self.num_topk, max(self.num_experts // group_size, 1)))
+        if self.num_max_recv_tokens > 0:
+            rows = min(rows, self.num_max_recv_tokens)
         body = 2 * rows * self.per_row_bytes(hidden_bytes)  # two epoch parities
         return FIXED_BYTES + align_up(body, REGION_ALIGN) + 16 * REGION_ALIGN * 2
 

@@ -153,14 +153,16 @@ def shutdown() -> None:
 
 
 def run_main(main) -> None:
-    """Run a CLI `main() -> int`; on any exception print it with the rank and leave the process
-    at once (exit code 1) so that the launcher tears the other ranks down instead of letting them
-    wait inside a collective. Parity: the top-level handler of `DeepEP_v1/deepep_v1_dispatch.py:384-394`."""
+    """Run a CLI `main() -> int` and leave through the interpreter's normal shut-down with its
+    return value as the exit code. Only on an exception does the process leave at once (exit code
+    1, after printing the traceback with the rank), so that the launcher tears the other ranks
+    down instead of letting them wait inside a collective.
+    Parity: the top-level handler of `DeepEP_v1/deepep_v1_dispatch.py:384-394`."""
     import traceback
     try:
         code = main()
     except SystemExit as e:
-        code = e.code if isinstance(e.code, int) else 1
+        code = e.code if isinstance(e.code, int) else (0 if e.code is None else 1)
     except BaseException:
         sys.stdout.flush()
         print(f"[rank {os.environ.get('RANK', '0')}] fatal:", file=sys.stderr)
@@ -169,4 +171,4 @@ def run_main(main) -> None:
         os._exit(1)
     sys.stdout.flush()
     sys.stderr.flush()
-    os._exit(int(code or 0))
+    sys.exit(int(code or 0))

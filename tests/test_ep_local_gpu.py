@@ -147,6 +147,110 @@ def test_lost_peer_is_an_error_not_a_hang():
         g.destroy()
 
 
+def test_recorded_fault_is_raised_by_the_next_op_without_check_status():
+    """A time-out leaves its code in the status word AND in a mapped host word; the next public
+    op on the buffer raises it even though nobody called check_status()."""
+    from gpu_data_transfer_profile_b200.parallel.buffer import Buffer, EpTimeoutError
+    from gpu_data_transfer_profile_b200.parallel.symm import LocalWorld
+    T, H, E, K = 64, 256, 8, 2
+    buf = Buffer(None, 32 << 20, world=LocalWorld.make(1)[0], timeout_s=2.0)
+    try:
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        idx, w = O.make_routing(T, E, K, 3)
+        idx, w = idx.cuda(), w.cuda()
+        assert buf.probe_timeout(0.05, clear=False) == 8
+        with pytest.raises(EpTimeoutError):
+            buf.get_dispatch_layout(idx, E)
+        # the fault was consumed: the buffer works again
+        pr, _, pe, inr, _ = buf.get_dispatch_layout(idx, E)
+        rx, _, _, _, h, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, is_token_in_rank=inr,
+                                         num_tokens_per_expert=pe)
+        assert torch.equal(rx, x)
+        buf.check_status()
+    finally:
+        buf.destroy()
+
+
+def test_cached_dispatch_refuses_a_handle_made_for_another_layout():
+    from gpu_data_transfer_profile_b200.parallel.buffer import Buffer
+    from gpu_data_transfer_profile_b200.parallel.symm import LocalWorld
+    T, H, E, K = 64, 256, 8, 2
+    buf = Buffer(None, 32 << 20, world=LocalWorld.make(1)[0], timeout_s=2.0)
+    try:
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        idx, w = O.make_routing(T, E, K, 3)
+        idx, w = idx.cuda(), w.cuda()
+        pr, _, pe, inr, _ = buf.get_dispatch_layout(idx, E)
+        _, _, _, _, h, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, is_token_in_rank=inr,
+                                        num_tokens_per_expert=pe)
+        y, _, _, _, _, _ = buf.dispatch(x * 2, handle=h)          # same width: fine
+        assert torch.equal(y, x * 2)
+        with pytest.raises(ValueError):
+            buf.dispatch(x.float(), handle=h)                      # wider rows: other layout, smaller capacity
+        buf.check_status()
+    finally:
+        buf.destroy()
+
+
+def test_receive_bound_overflow_is_a_status_not_a_fault():
+    """`num_max_recv_tokens` caps the receive region; a routing that needs more rows ends in
+    status 6 and every out-of-range row is skipped."""
+    from gpu_data_transfer_profile_b200.parallel.buffer import Buffer, EpStatusError
+    from gpu_data_transfer_profile_b200.parallel.symm import LocalWorld
+    T, H, E, K = 96, 256, 8, 2
+    buf = Buffer(None, 32 << 20, world=LocalWorld.make(1)[0], timeout_s=2.0, num_max_recv_tokens=64)
+    try:
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        idx, w = O.make_routing(T, E, K, 3)
+        idx, w = idx.cuda(), w.cuda()
+        pr, _, pe, inr, _ = buf.get_dispatch_layout(idx, E)
+        with pytest.raises(EpStatusError):
+            buf.dispatch(x, topk_idx=idx, topk_weights=w, is_token_in_rank=inr, num_tokens_per_expert=pe)
+            buf.check_status()
+        torch.cuda.synchronize()
+        try:
+            buf.check_status()
+        except EpStatusError:
+            pass
+        # a smaller batch fits
+        x2, idx2, w2 = x[:48].contiguous(), idx[:48].contiguous(), w[:48].contiguous()
+        pr, _, pe, inr, _ = buf.get_dispatch_layout(idx2, E)
+        rx, _, _, _, h, _ = buf.dispatch(x2, topk_idx=idx2, topk_weights=w2, is_token_in_rank=inr,
+                                         num_tokens_per_expert=pe)
+        assert torch.equal(rx, x2)
+        buf.check_status()
+    finally:
+        buf.destroy()
+
+
+@pytest.mark.parametrize("chunks", [0, 1, 5, 32])
+def test_round_trip_for_several_combine_chunk_counts(chunks):
+    """The number of combine chunks only changes WHEN rows are returned and reduced, never what."""
+    from gpu_data_transfer_profile_b200.parallel.buffer import Buffer
+    R, T, H, E, K = 4, 150, 512, 32, 4
+    xs, idxs, ws = _mk(R, T, H, E, K, uneven=True, seed=5)
+    old = Buffer.combine_chunks
+    Buffer.combine_chunks = chunks
+    g = _group(R)
+    try:
+        cx, ci, cw = [x.cuda() for x in xs], [i.cuda() for i in idxs], [w.cuda() for w in ws]
+        ref = O.dispatch_rank_mode_ref(xs, idxs, ws, E)
+        for rep in range(3):
+            lays = g.get_dispatch_layout(ci, E)
+            outs = g.dispatch(cx, layouts=lays, topk_idx=ci, topk_weights=cw)
+            for d in range(R):
+                assert torch.equal(outs[d][0].cpu(), ref[d][0])
+            comb = g.combine([o[0] for o in outs], [o[4] for o in outs])
+            cref = O.combine_ref([r[0] for r in ref], [r[3] for r in ref], [r[4] for r in ref],
+                                 [x.shape[0] for x in xs])
+            for s in range(R):
+                torch.testing.assert_close(comb[s][0].cpu().float(), cref[s], atol=0.16, rtol=2e-2)
+        g.check_status()
+    finally:
+        g.destroy()
+        Buffer.combine_chunks = old
+
+
 def test_dispatch_without_host_sync_num_worst_tokens():
     """num_worst_tokens: outputs sized by the caller's bound, true count only on the device."""
     from gpu_data_transfer_profile_b200.parallel.buffer import Buffer

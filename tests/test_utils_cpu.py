@@ -185,3 +185,29 @@ def test_gemm_band_height_follows_the_reduction_length():
     assert G._band_rows(14336, 32 << 20) == 1024              # rounded down to a multiple of 256 rows
     assert G._band_rows(1 << 20, 32 << 20) == 256             # never below one 256-row tile
     assert G._band_rows(4096) == G._band_rows(4096, G.BAND_BYTES)
+
+
+def test_cumulative_counter_comparison_survives_the_32_bit_wrap():
+    """The low-latency arrival counters grow for the life of a buffer; the wait compares modulo
+    2^32, so it must stay correct when the target passes 0x7fffffff -> 0x80000000 and 2^32 -> 0."""
+    from gpu_data_transfer_profile_b200 import _ext
+    reached = _ext.load().counter_reached
+    assert reached(5, 5) and reached(6, 5) and not reached(4, 5)
+    # target just past the sign bit, counter still just below it: not reached (a signed `>=` says it is)
+    assert not reached(0x7FFFFFF0, 0x80000010)
+    assert reached(0x80000010, 0x80000010) and reached(0x80000090, 0x80000010)
+    assert not reached(0x7FFFFFFF, 0x80000000) and reached(0x80000000, 0x7FFFFFFF)
+    # across the unsigned wrap
+    assert not reached(0xFFFFFFF0, 0x00000010) and reached(0x00000010, 0xFFFFFFF0)
+    assert reached(0x00000010, 0x00000010)
+
+
+def test_control_area_blocks_have_shape_independent_positions():
+    """Flag words are epochs that are never reset, so their offsets must not move when the expert
+    count (and with it the size of the count matrices) changes."""
+    from gpu_data_transfer_profile_b200.parallel.buffer import _Carve
+    a = _Carve(64 << 20, 8, 256, 8, 1024, 2048, 2048)
+    b = _Carve(64 << 20, 2, 8, 2, 512, 1024, 1024)
+    assert (a.flags, a.chunk_flags, a.recv_bnd) == (b.flags, b.chunk_flags, b.recv_bnd)
+    assert a.recv_bnd[1] < a.counts[0] and a.counts[1] < a.ll_ctrl
+    assert _Carve(64 << 20, 8, 256, 8, 1024, 2048, 2048, max_recv_rows=100).cap == 100

@@ -66,6 +66,41 @@ def test_no_alloc_batched_copy_matches_regular_entry_point_twice():
             assert torch.equal(got[o:o + s], src[o:o + s])
 
 
+def test_no_alloc_batched_copy_accepts_the_full_table():
+    """Exactly 1024 copies (the limit) of 48 bytes each, with 16-byte gaps that must stay untouched."""
+    lib, fn = _lib()
+    n, size, pitch = 1024, 48, 64
+    src = _pattern(n * pitch, seed=9)
+    got = torch.full((n * pitch,), 253, dtype=torch.uint8, device="cuda")
+    rc = _call(fn, [got.data_ptr() + i * pitch for i in range(n)],
+               [src.data_ptr() + i * pitch for i in range(n)], [size] * n, ctas=1, threads=64)
+    assert rc == 0, lib.b200ep_noalloc_error_string(rc)
+    torch.cuda.synchronize()
+    g2, s2 = got.view(n, pitch), src.view(n, pitch)
+    assert torch.equal(g2[:, :size], s2[:, :size])
+    assert bool((g2[:, size:] == 253).all())
+
+
+def test_no_alloc_batched_copy_refuses_a_capturing_stream():
+    """The descriptors are uploaded from the callee's stack, so a captured call would replay
+    garbage: the entry point must refuse (-7) and issue nothing."""
+    lib, fn = _lib()
+    src = _pattern(256, seed=3)
+    dst = torch.full((256,), 253, dtype=torch.uint8, device="cuda")
+    assert _call(fn, [dst.data_ptr()], [src.data_ptr()], [256]) == 0     # first call on this device: outside capture
+    torch.cuda.synchronize()
+    dst.fill_(253)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        dst.add_(0)                                                       # something to capture
+        rc = _call(fn, [dst.data_ptr()], [src.data_ptr()], [256])
+    assert rc == -7 and b"captur" in lib.b200ep_noalloc_error_string(rc)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert bool((dst == 253).all())                                       # nothing was recorded for the copy
+
+
 def test_no_alloc_batched_copy_rejects_bad_arguments():
     lib, fn = _lib()
     buf = torch.zeros(64, dtype=torch.uint8, device="cuda")
