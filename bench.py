@@ -161,6 +161,43 @@ def main() -> int:
     err = ((out.float() - want).abs() - rel * want.abs()).max().item()
     ok = D.all_ranks_boolean(err <= (0.15 if args.fp8 else 0.13))
 
+    # ---- builder-written NCCL comparator: same tokens, same routing, same metric -------------
+    # One row per (token, destination rank) like the library; the row order, the split sizes and
+    # the receive counts are computed ONCE here, outside the timed region, so the timed step is
+    # only: permute (index_select) + all_to_all_single + identity expert + all_to_all_single +
+    # un-permute/reduce (index_add_). No host synchronisation inside the step.
+    in_rank = handle.is_token_in_rank
+    dst_tok = in_rank.t().contiguous().nonzero()            # rows sorted by destination, then token
+    gather_idx = dst_tok[:, 1].contiguous()
+    send_counts = in_rank.sum(0).tolist()
+    if world > 1:
+        sc = torch.tensor(send_counts, device=dev, dtype=torch.int64)
+        rc = torch.empty_like(sc)
+        torch.distributed.all_to_all_single(rc, sc)
+        recv_counts = rc.tolist()
+    else:
+        recv_counts = list(send_counts)
+    send_buf = torch.empty((int(sum(send_counts)), H), dtype=torch.bfloat16, device=dev)
+    recv_buf = torch.empty((int(sum(recv_counts)), H), dtype=torch.bfloat16, device=dev)
+    back_buf = torch.empty_like(send_buf)
+    nccl_out = torch.empty((T, H), dtype=torch.float32, device=dev)
+
+    def nccl_step():
+        torch.index_select(x, 0, gather_idx, out=send_buf)
+        if world > 1:
+            torch.distributed.all_to_all_single(recv_buf, send_buf, recv_counts, send_counts)
+            torch.distributed.all_to_all_single(back_buf, recv_buf, send_counts, recv_counts)
+        else:
+            recv_buf.copy_(send_buf)
+            back_buf.copy_(recv_buf)
+        nccl_out.zero_()
+        nccl_out.index_add_(0, gather_idx, back_buf.float())
+        return nccl_out
+
+    nccl = time_steps(nccl_step, max(min(args.steps, 50), 3), 3, flush=flush, before=before)
+    nccl_ms = nccl["max_rank_mean_ms"]
+    nccl_err = (nccl_step() - want).abs().max().item()
+
     # bytes that cross NVLink per rank and step (dispatch + combine, remote destinations only)
     remote = handle.is_token_in_rank.clone()
     remote[:, rank] = False
@@ -175,12 +212,20 @@ def main() -> int:
         line = {
             "metric": METRIC, "value": round(ms * 1e3, 2), "unit": "us", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5),
-            "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": round(ms / nccl_ms, 4) if nccl_ms > 0 else None,
+            "baseline": {"what": "builder-written NCCL comparator (NOT the reference): torch all_to_all_single "
+                                 "dispatcher on the same tokens and routing in this process, one row per "
+                                 "(token, destination rank), splits precomputed outside the timed step",
+                         "value_us": round(nccl_ms * 1e3, 2), "check_max_abs_err": round(nccl_err, 4),
+                         "note": "vs_baseline = value / this (below 1 = faster); the reference publishes no "
+                                 "dispatch/combine number"},
             "dtype": "fp8_e4m3 dispatch / bf16 combine" if args.fp8 else "bf16",
             "data": "synthetic (seeded N(0,1) tokens, seeded softmax top-k routing)",
             "config": {"model": MODEL, "global_batch": int(total_tokens), "seq_len": T,
                        "parallelism": f"ep{world}", "hidden": H, "experts": E, "topk": K,
                        "zipf_s": args.zipf, "l2": "flushed between steps (252 MiB write)",
+                       "combine": "pull form: rows are read from the peers' receive regions and reduced in one pass",
                        "receive": "zero-copy views of the symmetric receive region, "
                                   + ("sized by a host read of the count" if args.host_count else "num_worst_tokens = world x tokens (no host sync)"),
                        "num_sms_knob": Buffer.num_sms,
@@ -188,6 +233,7 @@ def main() -> int:
             "tokens_per_s": round(total_tokens / (ms * 1e-3), 1),
             "nvlink_gbs_per_rank": round(nv_bytes_max / (ms * 1e-3) / 1e9, 2),
             "nvlink_roofline_frac_of_770GBs": round(nv_bytes_max / 770e9 / (ms * 1e-3), 4) if world > 1 else None,
+            "nvlink_roofline_frac_of_900GBs": round(nv_bytes_max / 900e9 / (ms * 1e-3), 4) if world > 1 else None,
             "min_step_us": round(res["min_ms"] * 1e3, 2),
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"],
                        "reasons": clocks["reasons"]} if clocks else None,
@@ -196,7 +242,7 @@ def main() -> int:
                     "d2h_bytes_per_step": 4,
                     "pipelining": "inputs double-buffered: the H2D copy of step i+1 overlaps step i"},
             "gpu_launches": 4 * args.steps,
-            "launches_per_step": "layout_kernel, notify_send_kernel, dispatch_send_kernel, combine_kernel",
+            "launches_per_step": "layout_kernel, notify_send_kernel, dispatch_send_kernel, combine_pull_kernel",
             "symmetric_bytes_reserved_per_rank": buf.bytes_reserved,
             "check": "ok" if ok else f"FAIL max_err={err:.4f}",
             "impl": "ours",

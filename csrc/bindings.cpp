@@ -105,33 +105,29 @@ PeerPtrs make_peers(const std::vector<int64_t>& bases) {
   return p;
 }
 EpGeom make_geom(const std::vector<int64_t>& v) {
-  TORCH_CHECK(v.size() == 18, "geom needs 18 entries");
+  TORCH_CHECK(v.size() == 16, "geom needs 16 entries");
   EpGeom g{};
   g.rank = (int)v[0]; g.R = (int)v[1]; g.E = (int)v[2]; g.El = (int)v[3]; g.K = (int)v[4];
   g.T = (int)v[5]; g.mode = (int)v[6]; g.J = (int)v[7]; g.B = (int)v[8]; g.H = (int)v[9];
   g.cap = (int)v[10]; g.slot_cap = (int)v[11]; g.epoch = (int)v[12]; g.epoch_wait = (int)v[13];
-  g.nch = (int)v[14]; g.chunk_tokens = (int)v[15]; g.tail_wait = (int)v[16];
-  g.timeout_ns = (unsigned long long)v[17];
+  g.tail_wait = (int)v[14];
+  g.timeout_ns = (unsigned long long)v[15];
   TORCH_CHECK(g.R >= 1 && g.R <= kMaxRanks && g.J <= kMaxItemsPerToken && g.K <= kMaxItemsPerToken,
               "geometry out of range");
-  TORCH_CHECK(g.nch >= 0 && g.nch <= kMaxCombChunks, "combine chunk count out of range");
-  if (g.nch > 0)
-    TORCH_CHECK(g.chunk_tokens > 0 && g.chunk_tokens % kChunkTokens == 0 &&
-                (int64_t)g.chunk_tokens * g.nch >= g.T, "combine chunks do not cover the tokens");
   return g;
 }
 EpRegions make_regions(const std::vector<int64_t>& v) {
-  TORCH_CHECK(v.size() == 12, "regions needs 12 entries");
+  TORCH_CHECK(v.size() == 11, "regions needs 11 entries");
   EpRegions r{};
   r.flags = v[0]; r.counts = v[1]; r.recv_x = v[2]; r.recv_scales = v[3]; r.recv_topk_idx = v[4];
   r.recv_topk_w = v[5]; r.recv_meta = v[6]; r.recv_prob = v[7]; r.comb_x = v[8]; r.comb_w = v[9];
-  r.chunk_flags = v[10]; r.recv_bnd = v[11];
+  r.pull_info = v[10];
   return r;
 }
 // meta tensor layout: [n_recv, send_total, expert_cnt[El], expert_off[El+1], src_off[R+1],
-//                      send_base[B], comb_base[B], bnd[R][kBndStride]]
+//                      send_base[B], comb_base[B]]
 int64_t meta_ints(const EpGeom& g) {
-  return 2 + g.El + (g.El + 1) + (g.R + 1) + 2 * (int64_t)g.B + (int64_t)g.R * kBndStride;
+  return 2 + g.El + (g.El + 1) + (g.R + 1) + 2 * (int64_t)g.B;
 }
 EpMeta make_meta(torch::Tensor& meta, const EpGeom& g) {
   TORCH_CHECK(meta.is_cuda() && meta.scalar_type() == torch::kInt32 && meta.is_contiguous());
@@ -143,7 +139,6 @@ EpMeta make_meta(torch::Tensor& meta, const EpGeom& g) {
   m.recv_src_off = m.recv_expert_off + g.El + 1;
   m.send_base = m.recv_src_off + g.R + 1;
   m.comb_base = m.send_base + g.B;
-  m.bnd = m.comb_base + g.B;
   return m;
 }
 void check_launch(const char* what) { cuda_ok(cudaGetLastError(), what); }
@@ -159,8 +154,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("MAX_RANKS") = kMaxRanks;
   m.attr("NUM_CHANNELS") = (int)kNumChannels;
   m.attr("CHUNK_TOKENS") = kChunkTokens;
-  m.attr("MAX_COMB_CHUNKS") = kMaxCombChunks;
-  m.attr("BND_STRIDE") = kBndStride;
   m.def("counter_reached", [](uint32_t have, uint32_t want) { return counter_reached(have, want); });
   m.def("symm_alloc", &symm_alloc);
   m.def("symm_free", &symm_free);

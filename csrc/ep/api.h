@@ -28,7 +28,7 @@ void launch_barrier(const PeerPtrs& peers, long long flags_off, int rank, int R,
 
 // g.epoch = dispatch epoch to publish, g.epoch_wait = notify epoch to wait for (fresh dispatch),
 // g.tail_wait = 1 makes the last CTA wait for the peers' dispatch flags (never with several
-// virtual ranks on one GPU: use launch_dispatch_wait after all ranks' sends instead).
+// virtual ranks on one GPU: use launch_wait_flags on the dispatch channel after all ranks' sends).
 // host_word: mapped pinned ints [0]=notify epoch served, [1]=N_recv, [2..2+El) per-expert counts.
 void launch_dispatch_send(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers,
                           const EpMeta& m, const char* x, int row_bytes_in, bool fp8, bool cached,
@@ -37,36 +37,53 @@ void launch_dispatch_send(const EpGeom& g, const EpRegions& rg, const PeerPtrs& 
                           unsigned int* block_counter, int* host_word, int* status, int blocks,
                           cudaStream_t st, const float* scales_in = nullptr);
 
-void launch_dispatch_wait(const EpGeom& g, const EpRegions& rg, char* self_base, const EpMeta& m,
-                          int* status, cudaStream_t st);
+enum CombineRole : int { kCombineBoth = 0, kCombineSendOnly = 1, kCombineReduceOnly = 2 };
 
-enum CombineRole : int { kCombineFused = 0, kCombineSendOnly = 1, kCombineReduceOnly = 2 };
-
+// Push form of combine (see combine.cu). kCombineBoth: every CTA sends its share of the rows, then
+// waits for the peers' flags and reduces its share of the tokens (one process per GPU only).
 struct CombineArgs {
+  int role;                  // CombineRole
   // send role
   const int* n_recv_ptr;     // device: number of valid rows in x
   const int2* recv_meta;     // [n_recv] {slot at source, source rank}
   const char* x;             // [n_recv][row_bytes]
   int row_bytes;
   const float* topk_w;       // optional side values returned with the rows
-  const int* bnd;            // [R][kBndStride] chunk boundaries (rank mode) or nullptr
-  int* seg_count;            // [kMaxRanks*kMaxCombChunks] zero on entry, left at zero
   unsigned int* block_counter;  // zero on entry, left at zero
-  // role selection
-  unsigned int* ticket;      // zero on entry, left at zero
-  int n_send;                // CTAs in the send role (fused launch)
-  int role;                  // CombineRole
   // reduce role
+  int wait;                  // 1: wait for every rank's combine flag of g.epoch first
   const int* send_slot;      // [T][J]
   const float* weights;      // optional [T][J]
   char* out;                 // [T][H]
   float* out_topk_w;         // optional [T][K]
-  int wait_mode;             // 0 none, 1 one flag per rank (channel kChCombine), 2 per-chunk flags
 };
+
+// Number of SMs: the largest useful grid (CTAs have 1024 threads, one per SM).
+int combine_max_ctas();
 
 // dtype_code: 0 bf16, 1 fp16, 2 fp32 (element type of x / out).
 void launch_combine(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers, const CombineArgs& a,
                     int dtype_code, int* status, int blocks, cudaStream_t st);
+
+// Pull form of combine: the rows to be combined stay where their producer wrote them, inside the
+// producer's symmetric region; every rank tells its peers where (`publish`), waits for the peers'
+// announcements and then LOADS the rows of its own tokens over NVLink, reducing them in registers.
+// No slot region, no second pass over the rows, nothing left to do when the last row has arrived.
+struct CombinePullArgs {
+  long long x_off;           // byte offset of MY rows inside my region (published to the peers)
+  long long w_off;           // byte offset of my side values (float), or -1
+  long long n_rows;          // rows that peers may read from x_off
+  int publish;               // 1: announce x_off / w_off / n_rows and raise my flag on every peer
+  int wait;                  // 1: wait for every peer's announcement of this epoch
+  int pull;                  // 1: do the reduction (0 = announce only)
+  const int* send_row;       // [T][J] row of (token, item) at its destination
+  const long long* topk_idx; // [T][K] (expert mode: which rank holds item k)
+  const float* weights;      // optional [T][J]
+  char* out;                 // [T][H]
+  float* out_topk_w;         // optional [T][K]
+};
+void launch_combine_pull(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers,
+                         const CombinePullArgs& a, int dtype_code, int* status, int blocks, cudaStream_t st);
 
 void launch_signal(const PeerPtrs& peers, long long flags_off, int channel, int rank, int R,
                    int epoch, cudaStream_t st);

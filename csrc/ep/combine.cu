@@ -1,25 +1,25 @@
-// Normal-mode combine, standalone form: every received row is pushed back to its source
-// rank's combine slot with LSU peer stores, and the source reduces its slots ON ARRIVAL
-// (fp32 accumulation, optional per-item weights).
-// Replaces `Buffer.combine` as consumed by `DeepEP_v1/deepep_v1_combine.py:241-247` and the
-// index_add_ unpermute of `DeepEP_Megatron/test_deepep_moe_dispatch_combine.py:390-403`.
-// The fused form (fc2 GEMM epilogue storing tiles straight into the same slots) lives in
-// csrc/gemm and uses the reduce role below.
+// Normal-mode combine. Replaces `Buffer.combine` as consumed by
+// `DeepEP_v1/deepep_v1_combine.py:241-247` and the index_add_ unpermute of
+// `DeepEP_Megatron/test_deepep_moe_dispatch_combine.py:390-403`. Two forms:
 //
-// ONE kernel, two roles. A CTA takes a ticket when it starts: the first `n_send` tickets send,
-// the rest reduce (so the CTAs that are placed first are senders, whatever order the hardware
-// places them in: a sender never waits for anything, a reducer only waits for peers' senders).
-//   send role    rows are visited chunk by chunk of the SOURCE's token range (the dispatch
-//                told every destination where each source chunk starts in its receive region):
-//                all warps work on chunk 0 of every source before chunk 1, a per-segment counter
-//                finds the warp that stores a segment's last row, and that warp releases the
-//                (destination, chunk) flag on the source.
-//   reduce role  tokens in increasing order; before the first token of a chunk the warp waits
-//                (bounded) for that chunk's flag from every rank, then sums the token's slots.
-// The reduction of chunk c therefore runs while chunk c+1 is still on the wire; only the last
-// chunk's reduction is left when the last row arrives.
-// With several virtual ranks on one GPU the two roles are launched separately (all sends, then
-// all reduces), because a reducer must never be resident while the sender it waits for is not.
+// PULL (rows inside the producer's symmetric region, e.g. the zero-copy output of dispatch):
+//   every rank announces where its rows are, waits (bounded) for the peers' announcements and
+//   LOADS the rows of its own tokens over NVLink, reducing them in fp32 registers on the way:
+//   one pass, no slot region, nothing left to do when the last row has arrived.
+// PUSH (rows anywhere): every received row is stored into its slot on the source rank with LSU
+//   peer stores; when its own rows are out a CTA waits (bounded) for the peers' flags and reduces
+//   the slots of this rank's tokens. The fc2 GEMM epilogue of csrc/gemm stores its tiles into the
+//   same slots and is followed by the reduce role alone.
+//
+// What was measured and dropped: cutting the push into token chunks with one flag per chunk, so
+// that the reduction of chunk c overlaps the arrival of chunk c+1. Any release fence on an SM
+// whose store queue is full of NVLink stores drains that queue first (tens of microseconds at a
+// per-SM share of the link of about 5 GB/s); with 8 ranks the send went from 413 to 587 us with
+// one fence per CTA and chunk and to 654 us with the reduction running beside it, against 519 us
+// for send-then-reduce. The pull form gets the overlap without any fence.
+//
+// One CTA of 1024 threads per SM. With several virtual ranks on one GPU the halves that wait for
+// peers are launched after the halves they wait for (all announcements / sends first).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "ep.cuh"
@@ -27,8 +27,9 @@
 
 namespace b200ep {
 
-constexpr int kCombWarps = 16;
+constexpr int kCombWarps = 32;   // one CTA of 1024 threads per SM
 constexpr int kCUnroll = 4;
+constexpr int kRUnroll = 4;      // vectors per lane in flight per contributor when reducing
 
 // ---- element helpers -------------------------------------------------------------------
 template <typename T> struct Vec16;
@@ -91,7 +92,7 @@ template <> struct Vec16<float> {
 };
 
 
-// ---- send role ---------------------------------------------------------------------------
+// ---- push form: send role ------------------------------------------------------------------
 __device__ __forceinline__ void combine_copy_row(const CombineArgs& a, const EpGeom& g, const EpRegions& rg,
                                                  const PeerPtrs& peers, int row, int lane, int* status) {
   const int2 meta = a.recv_meta[row];
@@ -124,109 +125,34 @@ __device__ __forceinline__ void combine_copy_row(const CombineArgs& a, const EpG
 }
 
 __device__ void combine_send_role(const CombineArgs& a, const EpGeom& g, const EpRegions& rg,
-                                  const PeerPtrs& peers, int si, int n_send, int* s_prefix, int* status) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // slice index: consecutive work items (= neighbouring rows = same peer) land on DIFFERENT CTAs,
-  // so every SM stores to a mix of peers and local memory instead of one SM group per peer
-  const int gw = warp * n_send + si, nw = n_send * kCombWarps;
+                                  const PeerPtrs& peers, int* status) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  // item index: neighbouring rows (same peer: rows are grouped by source rank or by expert) land on
+  // DIFFERENT CTAs, so every SM stores to a mix of peers instead of one SM group per peer; a warp's
+  // rows are spread over the whole range, so at any instant all peers are addressed in proportion
+  const int gw = warp * gridDim.x + blockIdx.x, nw = gridDim.x * nwarps;
   int n = *a.n_recv_ptr;
   if (n > g.cap) n = g.cap;
-  if (n < 0) n = 0;
-
-  if (a.bnd == nullptr || g.nch <= 0) {
-    // One flag per rank at the end. Rows are grouped by source rank (or by expert), so each warp
-    // takes one contiguous slice of the row range: at any instant the running warps cover the
-    // whole range, i.e. every peer at once in proportion to its share.
-    const int per_warp = (n + nw - 1) / nw;
-    const int i_end = min(n, (gw + 1) * per_warp);
-    for (int i = gw * per_warp; i < i_end; ++i) combine_copy_row(a, g, rg, peers, i, lane, status);
-    if (last_block_arrive(a.block_counter, n_send)) {
-      if ((int)threadIdx.x < g.R) {
-        int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + rg.flags) +
-                    kChCombine * kMaxRanks + g.rank;
-        st_release_sys(flag, g.epoch);
-      }
-    }
-    return;
-  }
-
-  // Segment (c, s) = rows of source s whose token lies in chunk c; visiting order (c, s, row).
-  const int R = g.R, nseg = g.nch * R;
-  for (int i = threadIdx.x; i < nseg; i += blockDim.x) {
-    const int c = i / R, s = i % R;
-    int lo = a.bnd[s * kBndStride + c], hi = a.bnd[s * kBndStride + c + 1];
-    lo = max(0, min(lo, n));
-    hi = max(lo, min(hi, n));
-    s_prefix[i] = hi - lo;
-  }
-  __syncthreads();
-  if (si == 0) {
-    // a chunk without rows for some source still has to be announced to that source
-    for (int i = threadIdx.x; i < nseg; i += blockDim.x) {
-      if (s_prefix[i] == 0) {
-        int* flag = reinterpret_cast<int*>(peers.base[i % R] + rg.chunk_flags) + g.rank * kMaxCombChunks + i / R;
-        st_release_sys(flag, g.epoch);
-      }
-    }
-  }
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    // exclusive scan in place; s_prefix[nseg] = total
-    int carry = 0;
-    for (int i0 = 0; i0 < nseg; i0 += 32) {
-      const int i = i0 + lane;
-      const int v = i < nseg ? s_prefix[i] : 0;
-      int incl = v;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int x = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += x;
-      }
-      if (i < nseg) s_prefix[i] = carry + incl - v;
-      carry += __shfl_sync(0xffffffffu, incl, 31);
-    }
-    if (lane == 0) s_prefix[nseg] = carry;
-  }
-  __syncthreads();
-  const int total = s_prefix[nseg];
-  for (int i = gw; i < total; i += nw) {
-    // last segment whose start is <= i (segments of size 0 share their start with the next one)
-    int lo = 0, hi = nseg;
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (s_prefix[mid] <= i) lo = mid; else hi = mid;
-    }
-    const int seg = lo, c = seg / R, s = seg % R;
-    const int start = max(0, min(a.bnd[s * kBndStride + c], n));
-    combine_copy_row(a, g, rg, peers, start + (i - s_prefix[seg]), lane, status);
-    __syncwarp();
-    if (lane == 0) {
-      // this warp's stores are system-visible before it counts the row; the warp that counts the
-      // segment's last row acquires the others' and releases the flag on the source
-      fence_acq_rel_sys();
-      const int size = s_prefix[seg + 1] - s_prefix[seg];
-      const int done = atomicAdd(&a.seg_count[seg], 1) + 1;
-      if (done == size) {
-        asm volatile("fence.acq_rel.gpu;" ::: "memory");
-        a.seg_count[seg] = 0;
-        int* flag = reinterpret_cast<int*>(peers.base[s] + rg.chunk_flags) + g.rank * kMaxCombChunks + c;
-        st_release_sys(flag, g.epoch);
-      }
+  for (int i = gw; i < n; i += nw) combine_copy_row(a, g, rg, peers, i, lane, status);
+  if (last_block_arrive(a.block_counter, gridDim.x)) {
+    if ((int)threadIdx.x < g.R) {
+      int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + rg.flags) +
+                  kChCombine * kMaxRanks + g.rank;
+      st_release_sys(flag, g.epoch);
     }
   }
 }
 
-// ---- reduce role -------------------------------------------------------------------------
-// warp per token: out[t] = sum_j w[t][j] * comb_x[slot[t][j]]  (w = 1 when absent).
+// ---- push form: reduce role ----------------------------------------------------------------
+// Work item = (token, part of the row): out[t] = sum_j w[t][j] * comb_x[slot[t][j]]  (w = 1 when absent).
 template <typename T>
 __device__ void combine_reduce_role(const CombineArgs& a, const EpGeom& g, const EpRegions& rg,
-                                    char* self_base, int ri, int n_red, int* status) {
+                                    char* self_base, int* status) {
   __shared__ int s_slot[kCombWarps][kMaxItemsPerToken];
   __shared__ float s_w[kCombWarps][kMaxItemsPerToken];
   __shared__ int s_ok;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool by_chunk = a.wait_mode == 2 && g.nch > 0;
-  if (a.wait_mode == 1 || (a.wait_mode == 2 && !by_chunk)) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  if (a.wait) {
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
     if ((int)threadIdx.x < g.R) {
@@ -239,22 +165,18 @@ __device__ void combine_reduce_role(const CombineArgs& a, const EpGeom& g, const
   const int J = g.J;
   const int row_bytes = g.H * (int)sizeof(T);
   const int nvec = row_bytes >> 4;
+  // a row is cut into up to 4 parts of at least 128 vectors, one warp each (shorter dependent chains)
+  int parts = nvec / 128;
+  parts = parts < 1 ? 1 : (parts > 4 ? 4 : parts);
+  if (parts == 3) parts = 2;
+  if (nwarps % parts) parts = 1;
+  const int part_vec = (nvec + parts - 1) / parts;
+  const int tok_per_round = nwarps / parts;
+  const int part = warp % parts, tok_in_cta = warp / parts;
   const char* comb = self_base + rg.comb_x;
   const float* comb_w = reinterpret_cast<const float*>(self_base + rg.comb_w);
-  const int* cflags = reinterpret_cast<const int*>(self_base + rg.chunk_flags);
-  const int gw = warp * n_red + ri, nw = n_red * kCombWarps;
-  int cur_chunk = -1;
-  for (int t = gw; t < g.T; t += nw) {
-    if (by_chunk) {
-      const int c = min(t / g.chunk_tokens, g.nch - 1);
-      if (c != cur_chunk) {
-        bool ok = true;
-        if (lane < g.R)
-          ok = wait_flag_ge(cflags + lane * kMaxCombChunks + c, g.epoch, g.timeout_ns, status, kTimeoutCombine);
-        if (!__all_sync(0xffffffffu, ok)) return;
-        cur_chunk = c;
-      }
-    }
+  const int per_round = gridDim.x * tok_per_round;
+  for (int t = blockIdx.x * tok_per_round + tok_in_cta; t < g.T; t += per_round) {
     int slot = -1;
     if (lane < J) {
       slot = a.send_slot[(size_t)t * J + lane];
@@ -264,18 +186,36 @@ __device__ void combine_reduce_role(const CombineArgs& a, const EpGeom& g, const
     }
     const unsigned vmask = __ballot_sync(0xffffffffu, slot >= 0);
     __syncwarp();
-    for (int v = lane; v < nvec; v += 32) {
-      float acc[Vec16<T>::N];
+    const int v_end = min(nvec, (part + 1) * part_vec);
+    // kRUnroll vectors per lane and contributor are loaded together (independent loads in flight),
+    // then accumulated in fp32; contributors are visited one after the other.
+    for (int v0 = part * part_vec + lane; v0 < v_end; v0 += 32 * kRUnroll) {
+      float acc[kRUnroll][Vec16<T>::N];
 #pragma unroll
-      for (int q = 0; q < Vec16<T>::N; ++q) acc[q] = 0.f;
+      for (int u = 0; u < kRUnroll; ++u)
+#pragma unroll
+        for (int q = 0; q < Vec16<T>::N; ++q) acc[u][q] = 0.f;
       for (unsigned mm = vmask; mm; mm &= mm - 1) {
         const int j = __ffs(mm) - 1;
-        const uint4 val = ld_global_v4(comb + (size_t)s_slot[warp][j] * row_bytes + ((size_t)v << 4));
-        Vec16<T>::acc(acc, val, s_w[warp][j]);
+        const char* rowp = comb + (size_t)s_slot[warp][j] * row_bytes;
+        const float wj = s_w[warp][j];
+        uint4 val[kRUnroll];
+#pragma unroll
+        for (int u = 0; u < kRUnroll; ++u) {
+          const int v = v0 + u * 32;
+          if (v < v_end) val[u] = ld_global_v4(rowp + ((size_t)v << 4));
+        }
+#pragma unroll
+        for (int u = 0; u < kRUnroll; ++u)
+          if (v0 + u * 32 < v_end) Vec16<T>::acc(acc[u], val[u], wj);
       }
-      st_global_v4(a.out + (size_t)t * row_bytes + ((size_t)v << 4), Vec16<T>::pack(acc));
+#pragma unroll
+      for (int u = 0; u < kRUnroll; ++u) {
+        const int v = v0 + u * 32;
+        if (v < v_end) st_global_v4(a.out + (size_t)t * row_bytes + ((size_t)v << 4), Vec16<T>::pack(acc[u]));
+      }
     }
-    if (a.out_topk_w != nullptr) {
+    if (a.out_topk_w != nullptr && part == 0) {
       if (g.mode == 0) {
         // rank mode: [T,K] = sum over destination ranks of the K side values of each row
         if (lane < g.K) {
@@ -294,29 +234,17 @@ __device__ void combine_reduce_role(const CombineArgs& a, const EpGeom& g, const
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kCombWarps * 32, 2)
+__global__ void __launch_bounds__(kCombWarps * 32, 1)
 combine_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, CombineArgs a, int* status) {
-  __shared__ int s_prefix[kMaxRanks * kMaxCombChunks + 1];
-  __shared__ unsigned int s_ticket;
-  unsigned int tk = blockIdx.x;
-  if (a.role == kCombineFused) {
-    if (threadIdx.x == 0) {
-      const unsigned int got = atomicAdd(a.ticket, 1u);
-      if (got == gridDim.x - 1) *a.ticket = 0u;      // every CTA has drawn: ready for the next launch
-      s_ticket = got;
-    }
-    __syncthreads();
-    tk = s_ticket;
-  }
-  const bool sender = a.role == kCombineSendOnly || (a.role == kCombineFused && (int)tk < a.n_send);
-  if (sender) {
-    combine_send_role(a, g, rg, peers, (int)tk, a.role == kCombineFused ? a.n_send : (int)gridDim.x,
-                      s_prefix, status);
-  } else {
-    const int ri = a.role == kCombineFused ? (int)tk - a.n_send : (int)tk;
-    const int n_red = a.role == kCombineFused ? (int)gridDim.x - a.n_send : (int)gridDim.x;
-    combine_reduce_role<T>(a, g, rg, peers.base[g.rank], ri, n_red, status);
-  }
+  if (a.role != kCombineReduceOnly) combine_send_role(a, g, rg, peers, status);
+  if (a.role != kCombineSendOnly) combine_reduce_role<T>(a, g, rg, peers.base[g.rank], status);
+}
+
+int combine_max_ctas() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 1;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) return 1;
+  return sms;
 }
 
 void launch_combine(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers, const CombineArgs& a,
@@ -328,6 +256,134 @@ void launch_combine(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers,
     combine_kernel<__half><<<blocks, kCombWarps * 32, 0, st>>>(g, rg, peers, a, status);
   else
     combine_kernel<float><<<blocks, kCombWarps * 32, 0, st>>>(g, rg, peers, a, status);
+}
+
+// ---- pull form -----------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kCombWarps * 32, 1)
+combine_pull_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, CombinePullArgs a, int* status) {
+  __shared__ int s_row[kCombWarps][kMaxItemsPerToken];
+  __shared__ int s_src[kCombWarps][kMaxItemsPerToken];
+  __shared__ float s_w[kCombWarps][kMaxItemsPerToken];
+  __shared__ long long s_info[kMaxRanks][4];
+  __shared__ int s_ok;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  char* self_base = peers.base[g.rank];
+  if (a.publish && blockIdx.x == 0 && (int)threadIdx.x < g.R) {
+    // rows were written by earlier kernels of this stream: complete and visible at this point
+    long long* info = reinterpret_cast<long long*>(peers.base[threadIdx.x] + rg.pull_info) + g.rank * 4;
+    info[0] = a.x_off;
+    info[1] = a.w_off;
+    info[2] = a.n_rows;
+    int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + rg.flags) + kChCombine * kMaxRanks + g.rank;
+    st_release_sys(flag, g.epoch);
+  }
+  if (!a.pull) return;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < g.R) {
+    const int* flags = reinterpret_cast<const int*>(self_base + rg.flags) + kChCombine * kMaxRanks;
+    if (a.wait && !wait_flag_ge(flags + threadIdx.x, g.epoch, g.timeout_ns, status, kTimeoutCombine)) s_ok = 0;
+    const long long* info = reinterpret_cast<const long long*>(self_base + rg.pull_info) + threadIdx.x * 4;
+    for (int q = 0; q < 3; ++q) s_info[threadIdx.x][q] = __ldcg(&info[q]);
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int J = g.J;
+  const int row_bytes = g.H * (int)sizeof(T);
+  const int nvec = row_bytes >> 4;
+  int parts = nvec / 128;
+  parts = parts < 1 ? 1 : (parts > 4 ? 4 : parts);
+  if (parts == 3) parts = 2;
+  if (nwarps % parts) parts = 1;
+  const int part_vec = (nvec + parts - 1) / parts;
+  const int tok_per_round = nwarps / parts;
+  const int part = warp % parts, tok_in_cta = warp / parts;
+  // consecutive (token, part) items land on different CTAs: every SM reads from a mix of peers
+  const int per_round = gridDim.x * tok_per_round;
+  for (int t = tok_in_cta * gridDim.x + blockIdx.x; t < g.T; t += per_round) {
+    int row = -1;
+    if (lane < J) {
+      row = a.send_row[(size_t)t * J + lane];
+      int d = lane;
+      if (g.mode == 1) {
+        const long long e = a.topk_idx[(size_t)t * g.K + lane];
+        d = (e >= 0 && e < g.E) ? (int)(e / g.El) : -1;
+      }
+      if (row >= 0 && (d < 0 || (long long)row >= s_info[d][2] || s_info[d][0] < 0)) {
+        set_status(status, kOverflowSlots);       // the peer did not announce that many rows
+        row = -1;
+      }
+      s_row[warp][lane] = row;
+      s_src[warp][lane] = d;
+      s_w[warp][lane] = a.weights ? a.weights[(size_t)t * J + lane] : 1.f;
+    }
+    const unsigned vmask = __ballot_sync(0xffffffffu, row >= 0);
+    __syncwarp();
+    const int v_end = min(nvec, (part + 1) * part_vec);
+    for (int v0 = part * part_vec + lane; v0 < v_end; v0 += 32 * kRUnroll) {
+      float acc[kRUnroll][Vec16<T>::N];
+#pragma unroll
+      for (int u = 0; u < kRUnroll; ++u)
+#pragma unroll
+        for (int q = 0; q < Vec16<T>::N; ++q) acc[u][q] = 0.f;
+      for (unsigned mm = vmask; mm; mm &= mm - 1) {
+        const int j = __ffs(mm) - 1;
+        const int d = s_src[warp][j];
+        const char* rowp = peers.base[d] + s_info[d][0] + (size_t)s_row[warp][j] * row_bytes;
+        const float wj = s_w[warp][j];
+        uint4 val[kRUnroll];
+#pragma unroll
+        for (int u = 0; u < kRUnroll; ++u) {
+          const int v = v0 + u * 32;
+          if (v < v_end) val[u] = ld_global_v4(rowp + ((size_t)v << 4));   // coherent path: another GPU wrote these rows
+        }
+#pragma unroll
+        for (int u = 0; u < kRUnroll; ++u)
+          if (v0 + u * 32 < v_end) Vec16<T>::acc(acc[u], val[u], wj);
+      }
+#pragma unroll
+      for (int u = 0; u < kRUnroll; ++u) {
+        const int v = v0 + u * 32;
+        if (v < v_end) st_global_v4(a.out + (size_t)t * row_bytes + ((size_t)v << 4), Vec16<T>::pack(acc[u]));
+      }
+    }
+    if (a.out_topk_w != nullptr && part == 0) {
+      // side values: K floats per row in rank mode (summed over the destinations), one in expert mode
+      if (g.mode == 0) {
+        if (lane < g.K) {
+          float s = 0.f;
+          for (unsigned mm = vmask; mm; mm &= mm - 1) {
+            const int j = __ffs(mm) - 1, d = s_src[warp][j];
+            const float* wp = reinterpret_cast<const float*>(peers.base[d] + s_info[d][1]);
+            s += wp[(size_t)s_row[warp][j] * g.K + lane];
+          }
+          a.out_topk_w[(size_t)t * g.K + lane] = s;
+        }
+      } else if (lane < J) {
+        float v = 0.f;
+        if (row >= 0) {
+          const int d = s_src[warp][lane];
+          v = reinterpret_cast<const float*>(peers.base[d] + s_info[d][1])[row];
+        }
+        a.out_topk_w[(size_t)t * J + lane] = v;
+      }
+    }
+    __syncwarp();
+  }
+}
+
+void launch_combine_pull(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers,
+                         const CombinePullArgs& a, int dtype_code, int* status, int blocks, cudaStream_t st) {
+  if (blocks < 1) blocks = 1;
+  const int threads = a.pull ? kCombWarps * 32 : 32;
+  if (!a.pull) blocks = 1;
+  if (dtype_code == 0)
+    combine_pull_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(g, rg, peers, a, status);
+  else if (dtype_code == 1)
+    combine_pull_kernel<__half><<<blocks, threads, 0, st>>>(g, rg, peers, a, status);
+  else
+    combine_pull_kernel<float><<<blocks, threads, 0, st>>>(g, rg, peers, a, status);
 }
 
 // Signal only (used when a fused GEMM epilogue has already stored the rows).

@@ -11,8 +11,7 @@
 //                         give, per bucket, the first row at the destination (`send_base`) and
 //                         the first slot of this rank's combine region (`comb_base`), kept in
 //                         shared memory. CTA 0 also writes the receive-side tables of the
-//                         handle, the receive count for the host, and (rank mode) tells every
-//                         destination at which row each of this rank's token chunks starts.
+//                         handle and the receive count for the host.
 //   body                  one warp per token, 16-byte stores to every destination.
 //   epilogue (last CTA)   release this rank's dispatch flag on every peer; when the kernel is
 //                         not one of several virtual ranks on one GPU, also wait (bounded) for
@@ -93,11 +92,11 @@ __device__ bool dispatch_prologue(const EpGeom& g, const EpRegions& rg, char* se
   return true;
 }
 
-// CTA 0 only: receive-side tables of the handle, host words, overflow checks, chunk boundaries.
+// CTA 0 only: receive-side tables of the handle, host words, overflow checks.
 __device__ void dispatch_publish_meta(const EpGeom& g, const EpRegions& rg, const PeerPtrs& peers,
                                       char* self_base, const EpMeta& m, const int* s_send_base,
-                                      const int* s_comb_base, const int* chunk_base,
-                                      volatile int* host_word, int* status, bool ok) {
+                                      const int* s_comb_base, volatile int* host_word, int* status,
+                                      bool ok) {
   __shared__ int s_cnt[kMaxRanks + 1];
   const int R = g.R, E = g.E, El = g.El, V = g.R + g.E, me = g.rank, B = g.B;
   if (!ok) {
@@ -153,44 +152,14 @@ __device__ void dispatch_publish_meta(const EpGeom& g, const EpRegions& rg, cons
       host_word[0] = g.epoch_wait;
     }
   }
-  if (g.mode == 0 && g.nch > 0) {
-    // first row, on destination d, of each of my token chunks (chunk_base is in 32-token units)
-    const int C32 = g.T > 0 ? (g.T + kChunkTokens - 1) / kChunkTokens : 1;
-    const int per = g.chunk_tokens / kChunkTokens;
-    for (int i = threadIdx.x; i < R * (g.nch + 1); i += blockDim.x) {
-      const int d = i / (g.nch + 1), c = i % (g.nch + 1);
-      const int cc = c * per;
-      const int within = (cc < C32 && g.T > 0) ? __ldcg(&chunk_base[(size_t)cc * B + d]) : __ldcg(&M[me * V + d]);
-      int* dst = reinterpret_cast<int*>(peers.base[d] + rg.recv_bnd) + me * kBndStride + c;
-      st_relaxed_sys(dst, s_send_base[d] + within);
-    }
-  }
 }
 
-// One CTA: bounded wait for every peer's dispatch flag, then keep a private copy of the chunk
-// boundaries (the region's copy is overwritten two dispatches later; the handle may live longer).
-__device__ void dispatch_tail_wait(const EpGeom& g, const EpRegions& rg, char* self_base,
-                                   const EpMeta& m, int* status) {
-  __shared__ int s_ok2;
-  if (threadIdx.x == 0) s_ok2 = 1;
-  __syncthreads();
+// Bounded wait for every peer's dispatch flag (R threads of one CTA).
+__device__ void dispatch_tail_wait(const EpGeom& g, const EpRegions& rg, char* self_base, int* status) {
   if ((int)threadIdx.x < g.R) {
     const int* flags = reinterpret_cast<const int*>(self_base + rg.flags) + kChDispatch * kMaxRanks;
-    if (!wait_flag_ge(flags + threadIdx.x, g.epoch, g.timeout_ns, status, kTimeoutDispatch)) s_ok2 = 0;
+    wait_flag_ge(flags + threadIdx.x, g.epoch, g.timeout_ns, status, kTimeoutDispatch);
   }
-  __syncthreads();
-  if (!s_ok2 || m.bnd == nullptr || g.mode != 0 || g.nch <= 0) return;
-  const int* src = reinterpret_cast<const int*>(self_base + rg.recv_bnd);
-  for (int i = threadIdx.x; i < g.R * kBndStride; i += blockDim.x) m.bnd[i] = __ldcg(&src[i]);
-}
-
-__global__ void dispatch_wait_kernel(EpGeom g, EpRegions rg, char* self_base, EpMeta m, int* status) {
-  dispatch_tail_wait(g, rg, self_base, m, status);
-}
-
-void launch_dispatch_wait(const EpGeom& g, const EpRegions& rg, char* self_base, const EpMeta& m,
-                          int* status, cudaStream_t st) {
-  dispatch_wait_kernel<<<1, 256, 0, st>>>(g, rg, self_base, m, status);
 }
 
 template <int MODE, bool FP8, bool CACHED>
@@ -219,8 +188,7 @@ dispatch_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, EpMeta m,
     // still raised so that healthy peers are not kept waiting by this rank).
     const bool ok = dispatch_prologue(g, rg, self_base, s_send_base, s_comb_base, dyn + 2 * g.B, status);
     if (blockIdx.x == 0)
-      dispatch_publish_meta(g, rg, peers, self_base, m, s_send_base, s_comb_base, chunk_base, host_word,
-                            status, ok);
+      dispatch_publish_meta(g, rg, peers, self_base, m, s_send_base, s_comb_base, host_word, status, ok);
     if (!ok) n_tokens = 0;
   }
 
@@ -339,7 +307,7 @@ dispatch_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, EpMeta m,
                   kChDispatch * kMaxRanks + g.rank;
       st_release_sys(flag, g.epoch);
     }
-    if (g.tail_wait) dispatch_tail_wait(g, rg, self_base, m, status);
+    if (g.tail_wait) dispatch_tail_wait(g, rg, self_base, status);
   }
 }
 

@@ -25,16 +25,12 @@ enum Channel : int {
   kChBarrier = 3,
   kChLLDispatch = 4,
   kChLLCombine = 5,
+  kChLLPull = 6,      // low-latency combine, pull form: one arrival per call and rank
   kNumChannels = 8,
 };
 
 constexpr int kChunkTokens = 32;   // tokens per counting chunk (one warp of notify_send)
 constexpr int kMaxItemsPerToken = 32;
-// Combine chunks: every rank cuts ITS token range into `nch` equal chunks (a multiple of 32
-// tokens each). A destination returns the rows of a source chunk by chunk and raises one flag per
-// (destination, chunk) on the source, so the source reduces chunk c while chunk c+1 still arrives.
-constexpr int kMaxCombChunks = 32;
-constexpr int kBndStride = kMaxCombChunks + 1;
 
 // Byte offsets inside every rank's symmetric region (same on all ranks). Offsets of
 // double-buffered regions are already resolved for this call's epoch parity by the host.
@@ -49,8 +45,7 @@ struct EpRegions {
   long long recv_prob;     // float [cap]
   long long comb_x;        // bytes [slot_cap][comb_row_bytes]
   long long comb_w;        // float [slot_cap][K]
-  long long chunk_flags;   // int   [kMaxRanks][kMaxCombChunks]  combine epoch in which rank d returned chunk c
-  long long recv_bnd;      // int   [kMaxRanks][kBndStride] (this parity): first receive row of (source, chunk)
+  long long pull_info;     // int64 [kMaxRanks][4]: where rank d keeps the rows that a pulling combine reads
 };
 
 struct EpGeom {
@@ -62,8 +57,6 @@ struct EpGeom {
   int slot_cap;  // combine slot capacity for this call
   int epoch;     // flag value to publish (dispatch / combine epoch; notify epoch in notify_send)
   int epoch_wait;  // dispatch_send: notify epoch whose count vectors the prologue waits for
-  int nch;         // combine chunks per rank (0 = one flag per rank at the end of the send)
-  int chunk_tokens;  // tokens per combine chunk on THIS rank (multiple of 32)
   int tail_wait;   // dispatch_send: 1 = the last CTA also waits for the peers' dispatch flags
   unsigned long long timeout_ns;
 };
@@ -78,7 +71,6 @@ struct EpMeta {
   int* send_base;         // [B]
   int* comb_base;         // [B]
   int* send_total;        // [1] number of slots used on this rank
-  int* bnd;               // [R][kBndStride] first receive row of (source, chunk) on THIS rank (rank mode)
 };
 
 }  // namespace b200ep

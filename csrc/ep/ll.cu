@@ -97,7 +97,7 @@ __device__ __forceinline__ void ll_arrive_on_peers(const LLParams& P, const Peer
 __global__ void __launch_bounds__(kLLThreads)
 ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
                         const long long* __restrict__ topk_idx, int* send_cnt_all, int* state,
-                        int* status) {
+                        int* status, int* __restrict__ send_slot) {
   __shared__ char* s_dst[kMaxItemsPerToken];
   __shared__ float* s_scl[kMaxItemsPerToken];
   __shared__ int s_n;
@@ -116,9 +116,11 @@ ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
     __syncthreads();
     if (threadIdx.x < P.K) {
       const long long e = topk_idx[(size_t)t * P.K + threadIdx.x];
+      int given = -1;
       if (e >= 0 && e < P.E) {
         const int slot = atomicAdd(&send_cnt[e], 1);
         if (slot < P.M) {
+          given = slot;
           const int d = (int)e / P.El, el = (int)e % P.El;
           const size_t row = ((size_t)el * P.R + P.rank) * P.M + slot;
           char* pb = peers.base[d];
@@ -133,6 +135,7 @@ ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
       } else if (e != -1) {
         set_status(status, kBadExpertIndex);
       }
+      if (send_slot != nullptr) send_slot[(size_t)t * P.K + threadIdx.x] = given;
     }
     __syncthreads();
     const int n = s_n;
@@ -367,6 +370,143 @@ ll_combine_recv_kernel(LLParams P, char* self_base, const long long* __restrict_
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// combine, pull form: announce, wait, load + reduce. One warp per (token, eighth of the row);
+// the rows of four experts are requested together, so a token costs two NVLink round trips.
+// ---------------------------------------------------------------------------------------
+constexpr int kPullGroup = 4;    // contributors whose loads are in flight together
+constexpr int kPullUnroll = 4;   // 16-byte vectors per lane and contributor
+
+__global__ void __launch_bounds__(kLLThreads)
+ll_combine_pull_kernel(LLParams P, PeerPtrs peers, int phase, const int* __restrict__ range,
+                       const int* __restrict__ send_slot, const long long* __restrict__ topk_idx,
+                       const float* __restrict__ topk_w, char* __restrict__ out, int* state, int* status) {
+  __shared__ int s_epoch;
+  __shared__ unsigned int s_target;
+  __shared__ int s_ok;
+  ll_stream_order();
+  // state: [0] committed epoch, [1] committed arrival target, [2],[3] the pair published by an
+  // announce-only launch, [4] CTAs of this launch that have finished
+  if (threadIdx.x == 0) {
+    if (phase == 2) {
+      s_epoch = *reinterpret_cast<volatile int*>(state + 2);
+      s_target = (unsigned int)*reinterpret_cast<volatile int*>(state + 3);
+    } else {
+      s_epoch = *reinterpret_cast<volatile int*>(state + 0) + 1;
+      s_target = (unsigned int)*reinterpret_cast<volatile int*>(state + 1) + 1u;
+      if (phase == 1) { state[2] = s_epoch; state[3] = (int)s_target; }
+    }
+    s_ok = 1;
+  }
+  __syncthreads();
+  const int epoch = s_epoch, par = epoch & 1;
+  const unsigned int target = s_target;
+  char* self_base = peers.base[P.rank];
+  if (phase != 2 && blockIdx.x == 0) {
+    // tell every source rank where, in my packed expert rows, its rows start
+    for (int i = threadIdx.x; i < P.R * P.El; i += blockDim.x) {
+      const int s = i / P.El, el = i % P.El;
+      int* dst = reinterpret_cast<int*>(peers.base[s] + P.range_tab[par]) + P.rank * P.El + el;
+      st_relaxed_sys(dst, range[((size_t)el * P.R + s) * 2]);
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < P.R) {
+      unsigned int* ctr = reinterpret_cast<unsigned int*>(peers.base[threadIdx.x] + P.flags) + kChLLPull * kMaxRanks + P.rank;
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ctr), "r"(1u) : "memory");
+    }
+  }
+  if (phase == 1) return;
+  if ((int)threadIdx.x < P.R) {
+    const int* flags = reinterpret_cast<const int*>(self_base + P.flags) + kChLLPull * kMaxRanks;
+    if (!wait_counter_reached(flags + threadIdx.x, target, P.timeout_ns, status, kTimeoutLowLatency)) s_ok = 0;
+  }
+  __syncthreads();
+  if (s_ok) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kLLThreads / 32;
+    const int row_bytes = P.H * 2;
+    const int nvec = row_bytes >> 4;
+    int parts = (nvec + 32 * kPullUnroll - 1) / (32 * kPullUnroll);   // one batch of loads per warp and contributor
+    if (parts < 1) parts = 1;
+    const int part_vec = (nvec + parts - 1) / parts;
+    const int* rtab = reinterpret_cast<const int*>(self_base + P.range_tab[par]);
+    const size_t cap = (size_t)P.R * P.M;
+    const int items = P.T * parts;
+    for (int it = blockIdx.x * nwarps + warp; it < items; it += gridDim.x * nwarps) {
+      const int t = it / parts, part = it % parts;
+      const int v_lo = part * part_vec, v_hi = min(nvec, v_lo + part_vec);
+      float acc[kPullUnroll][8];
+#pragma unroll
+      for (int u = 0; u < kPullUnroll; ++u)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[u][q] = 0.f;
+      for (int k0 = 0; k0 < P.K; k0 += kPullGroup) {
+        uint4 val[kPullGroup][kPullUnroll];
+        float wk[kPullGroup];
+#pragma unroll
+        for (int g = 0; g < kPullGroup; ++g) {
+          const int k = k0 + g;
+          wk[g] = 0.f;
+          if (k >= P.K) continue;
+          const long long e = topk_idx[(size_t)t * P.K + k];
+          const int slot = send_slot[(size_t)t * P.K + k];
+          if (e < 0 || e >= P.E || slot < 0 || slot >= P.M) continue;
+          const int d = (int)e / P.El, el = (int)e % P.El;
+          const int start = __ldcg(&rtab[d * P.El + el]);
+          if (start < 0 || (size_t)start + slot >= cap) {
+            if (lane == 0) set_status(status, kOverflowSlots);
+            continue;
+          }
+          wk[g] = topk_w ? topk_w[(size_t)t * P.K + k] : 1.f;
+          const char* rowp = peers.base[d] + P.comb_in + ((size_t)el * cap + start + slot) * row_bytes;
+#pragma unroll
+          for (int u = 0; u < kPullUnroll; ++u) {
+            const int v = v_lo + u * 32 + lane;
+            if (v < v_hi) val[g][u] = ld_global_v4(rowp + ((size_t)v << 4));
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < kPullGroup; ++g) {
+          if (wk[g] == 0.f) continue;
+#pragma unroll
+          for (int u = 0; u < kPullUnroll; ++u) {
+            if (v_lo + u * 32 + lane >= v_hi) continue;
+            const uint32_t uu[4] = {val[g][u].x, val[g][u].y, val[g][u].z, val[g][u].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              acc[u][2 * q] += wk[g] * bf16lo(uu[q]);
+              acc[u][2 * q + 1] += wk[g] * bf16hi(uu[q]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kPullUnroll; ++u) {
+        const int v = v_lo + u * 32 + lane;
+        if (v >= v_hi) continue;
+        uint4 o;
+        uint32_t* ou = &o.x;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(acc[u][2 * q], acc[u][2 * q + 1]);
+          ou[q] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        st_global_v4(out + (size_t)t * row_bytes + ((size_t)v << 4), o);
+      }
+    }
+  }
+  // the CTA that finishes last commits the epoch (every CTA has read the old one by then)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(reinterpret_cast<unsigned int*>(state + 4), 1u);
+    if (prev == gridDim.x - 1) {
+      state[4] = 0;
+      state[0] = epoch;
+      state[1] = (int)target;
+    }
+  }
+}
+
 // ---- launchers -------------------------------------------------------------------------
 // The dispatch send grid is ALWAYS P.G CTAs and the combine send grid ALWAYS (El, P.Gc / El):
 // receivers count arrivals, so the number of CTAs must be the same on every rank.
@@ -386,8 +526,9 @@ static void ll_launch(void (*kern)(KArgs...), dim3 grid, bool pdl, cudaStream_t 
 
 void launch_ll_dispatch_send(const LLParams& P, const PeerPtrs& peers, const char* x,
                              const long long* topk_idx, int* send_cnt, int* state, int* status,
-                             cudaStream_t st) {
-  ll_launch(ll_dispatch_send_kernel, dim3(P.G), P.pdl != 0, st, P, peers, x, topk_idx, send_cnt, state, status);
+                             cudaStream_t st, int* send_slot) {
+  ll_launch(ll_dispatch_send_kernel, dim3(P.G), P.pdl != 0, st, P, peers, x, topk_idx, send_cnt, state, status,
+            send_slot);
 }
 void launch_ll_dispatch_recv(const LLParams& P, char* self_base, char* out_x, float* out_scales,
                              int* out_src, int* out_count, int* out_range, int* state,
@@ -406,6 +547,13 @@ void launch_ll_combine_recv(const LLParams& P, char* self_base, const long long*
   int g = P.T < blocks ? P.T : blocks;
   if (g < 1) g = 1;
   ll_launch(ll_combine_recv_kernel, dim3(g), P.pdl != 0, st, P, self_base, topk_idx, topk_w, out, state, status);
+}
+
+void launch_ll_combine_pull(const LLParams& P, const PeerPtrs& peers, int phase, const int* range,
+                            const int* send_slot, const long long* topk_idx, const float* topk_w,
+                            char* out, int* state, int* status, cudaStream_t st) {
+  ll_launch(ll_combine_pull_kernel, dim3(phase == 1 ? 1 : P.G), P.pdl != 0, st, P, peers, phase, range,
+            send_slot, topk_idx, topk_w, out, state, status);
 }
 
 }  // namespace b200ep

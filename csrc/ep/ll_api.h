@@ -17,6 +17,8 @@ struct LLParams {
   long long recv_src[2];      // int [El][R][M]  (token << 5 | k)
   long long comb_x[2];        // bf16 [M][K][H]
   long long recv_tag[2];      // int [El][R][M]  epoch in which the slot was written
+  long long comb_in;          // bf16 [El][R*M][H]  expert output written in place (pull-form combine), one copy
+  long long range_tab[2];     // int [R][El]: first packed row, on rank d, of the rows that came from THIS rank
   int G;                      // CTAs of EVERY dispatch-send launch (same on all ranks)
   int Gc;                     // CTAs of EVERY combine-send launch (multiple of El)
   int signal_mode;            // 0: every send CTA signals every peer; 1: the last CTA does (see ll.cu)
@@ -25,14 +27,26 @@ struct LLParams {
 };
 
 // `state`: device int[6] per op (see ll.cu). `send_cnt`: device int[2*E], zero-initialised once.
+// send_slot (optional): int [M*K], receives the slot given to every item (t,k), -1 = not sent.
 void launch_ll_dispatch_send(const LLParams& P, const PeerPtrs& peers, const char* x,
                              const long long* topk_idx, int* send_cnt, int* state, int* status,
-                             cudaStream_t st);
+                             cudaStream_t st, int* send_slot = nullptr);
 void launch_ll_dispatch_recv(const LLParams& P, char* self_base, char* out_x, float* out_scales,
                              int* out_src, int* out_count, int* out_range, int* state,
                              int* status, int split, cudaStream_t st);
 void launch_ll_combine_send(const LLParams& P, const PeerPtrs& peers, const char* x, const int* src_info,
                             const int* count, int* state, int* status, cudaStream_t st);
+// Pull form of the low-latency combine: the expert output stays in the producers' regions
+// (`comb_in`, rows packed per local expert as `low_latency_dispatch` returned them); every rank
+// announces where the rows of each source start, then loads the K rows of each of its tokens over
+// NVLink and reduces them with the routing weights. phase 0: one launch; 1: announce only;
+// 2: wait + reduce (two launches only for several virtual ranks on one GPU).
+// range: int [El][R][2] (first packed row, count) from the dispatch handle; send_slot: int [M*K]
+// slot that dispatch gave to item (t,k), -1 = dropped. state: device int[6].
+void launch_ll_combine_pull(const LLParams& P, const PeerPtrs& peers, int phase, const int* range,
+                            const int* send_slot, const long long* topk_idx, const float* topk_w,
+                            char* out, int* state, int* status, cudaStream_t st);
+
 void launch_ll_combine_recv(const LLParams& P, char* self_base, const long long* topk_idx,
                             const float* topk_w, char* out, int* state, int* status,
                             int blocks, cudaStream_t st);

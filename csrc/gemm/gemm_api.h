@@ -37,6 +37,28 @@ struct GemmParams {
 int launch_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, GemmParams p,
                         const PeerPtrs& peers, int ctas, bool pair, cudaStream_t st);
 
+// Block-scaled fp8 grouped GEMM (csrc/gemm/grouped_gemm_fp8.cu).
+struct GemmFp8Params {
+  int El;                 // local experts
+  int N;                  // plain: output features; swiglu: F (gate and linear blocks of F weight rows each)
+  int K;                  // reduction length (multiple of 128)
+  int N_out;              // columns of the stored result (== N)
+  int w_rows;             // weight rows per expert (N, or 2F for swiglu); multiple of 128
+  int n_tiles, max_rows;  // filled by the launcher
+  int band_rows;          // activation rows per L2-resident band of the tile order (<= 0: 2048)
+  const int* expert_off;  // device [El+1]
+  const float* sa;        // f32 [rows, sa_ld]: scale of row r, reduction block kb at sa[r * sa_ld + kb]
+  long long sa_ld;
+  const float* sw;        // f32 [El, w_rows / 128, K / 128]
+  void* out;              // bf16 [rows, out_ld]
+  long long out_ld;
+  const float* row_prob;  // f32 [rows] or null (swiglu)
+  int* status;
+};
+// a: e4m3 [a_rows, K], w: e4m3 [El * w_rows, K], both on this GPU. epi: EPI_PLAIN or EPI_SWIGLU.
+int launch_grouped_gemm_fp8(const void* a, long long a_rows, const void* w, int epi, GemmFp8Params p, int ctas,
+                            cudaStream_t st);
+
 // Weight gradient of a grouped GEMM: dW[e] = G_e^T . X_e over the rows of local expert e.
 struct WgradParams {
   int El;                 // local experts
@@ -57,5 +79,11 @@ int launch_swiglu_fwd(const void* h, const float* p, void* act, const int* n_row
                       cudaStream_t st);
 int launch_swiglu_bwd(const void* h, const float* p, const void* dact, void* dh, float* dp, const int* n_rows_ptr,
                       int max_rows, int F, cudaStream_t st);
+
+// Ungated activation x prob pair (h: bf16 [rows, F]); kind: 0 gelu (erf form), 1 silu, 2 relu.
+int launch_act_fwd(const void* h, const float* p, void* act, const int* n_rows_ptr, int max_rows, int F, int kind,
+                   cudaStream_t st);
+int launch_act_bwd(const void* h, const float* p, const void* dact, void* dh, float* dp, const int* n_rows_ptr,
+                   int max_rows, int F, int kind, cudaStream_t st);
 
 }  // namespace b200ep

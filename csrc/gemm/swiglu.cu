@@ -110,4 +110,104 @@ int launch_swiglu_bwd(const void* h, const float* p, const void* dact, void* dh,
   return 0;
 }
 
+// ---------------------------------------------------------------------------------------
+// Ungated activations (gelu / silu / relu) x routing probability, forward and backward:
+//   act = f(h) * p[row],   dh = dact * p * f'(h),   dp[row] = sum_f dact * f(h)
+// kind: 0 gelu (erf form, as torch.nn.functional.gelu), 1 silu, 2 relu.
+// (`DeepEP_Megatron/test_deepep_moe_dispatch_combine.py:516-526` offers these beside swiglu.)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void act_eval(int kind, float x, float* f, float* df) {
+  if (kind == 0) {
+    const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
+    const float pdf = 0.39894228040143268f * __expf(-0.5f * x * x);
+    *f = x * cdf;
+    *df = cdf + x * pdf;
+  } else if (kind == 1) {
+    const float sig = 1.f / (1.f + __expf(-x));
+    *f = x * sig;
+    *df = sig * (1.f + x * (1.f - sig));
+  } else {
+    *f = x > 0.f ? x : 0.f;
+    *df = x > 0.f ? 1.f : 0.f;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+act_fwd_kernel(const char* __restrict__ h, const float* __restrict__ p, char* __restrict__ act,
+               const int* __restrict__ n_rows_ptr, int max_rows, int F, int kind) {
+  const int rows = n_rows_ptr ? min(*n_rows_ptr, max_rows) : max_rows;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float pr = p ? p[r] : 1.f;
+    const char* g = h + (size_t)r * F * 2;
+    char* o = act + (size_t)r * F * 2;
+    for (int v = threadIdx.x; v < F / 8; v += blockDim.x) {
+      float fg[8], fo[8];
+      unpack8(ld_global_nc_v4(g + ((size_t)v << 4)), fg);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float f, df;
+        act_eval(kind, fg[i], &f, &df);
+        fo[i] = f * pr;
+      }
+      st_global_v4(o + ((size_t)v << 4), pack8(fo));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+act_bwd_kernel(const char* __restrict__ h, const float* __restrict__ p, const char* __restrict__ dact,
+               char* __restrict__ dh, float* __restrict__ dp, const int* __restrict__ n_rows_ptr,
+               int max_rows, int F, int kind) {
+  __shared__ float s_part[8];
+  const int rows = n_rows_ptr ? min(*n_rows_ptr, max_rows) : max_rows;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float pr = p ? p[r] : 1.f;
+    const char* g = h + (size_t)r * F * 2;
+    const char* d = dact + (size_t)r * F * 2;
+    char* og = dh + (size_t)r * F * 2;
+    float acc = 0.f;
+    for (int v = threadIdx.x; v < F / 8; v += blockDim.x) {
+      float fg[8], fd[8], dg[8];
+      unpack8(ld_global_nc_v4(g + ((size_t)v << 4)), fg);
+      unpack8(ld_global_nc_v4(d + ((size_t)v << 4)), fd);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float f, df;
+        act_eval(kind, fg[i], &f, &df);
+        acc += fd[i] * f;
+        dg[i] = fd[i] * pr * df;
+      }
+      st_global_v4(og + ((size_t)v << 4), pack8(dg));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0 && dp != nullptr) {
+      float t = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += s_part[w];
+      dp[r] = t;
+    }
+    __syncthreads();
+  }
+}
+
+int launch_act_fwd(const void* h, const float* p, void* act, const int* n_rows_ptr, int max_rows, int F, int kind,
+                   cudaStream_t st) {
+  if (F <= 0 || F % 8 || max_rows < 0 || kind < 0 || kind > 2) return 1;
+  if (max_rows == 0) return 0;
+  act_fwd_kernel<<<min(max_rows, 148 * 16), 256, 0, st>>>(static_cast<const char*>(h), p, static_cast<char*>(act),
+                                                          n_rows_ptr, max_rows, F, kind);
+  return 0;
+}
+
+int launch_act_bwd(const void* h, const float* p, const void* dact, void* dh, float* dp, const int* n_rows_ptr,
+                   int max_rows, int F, int kind, cudaStream_t st) {
+  if (F <= 0 || F % 8 || max_rows < 0 || kind < 0 || kind > 2) return 1;
+  if (max_rows == 0) return 0;
+  act_bwd_kernel<<<min(max_rows, 148 * 16), 256, 0, st>>>(static_cast<const char*>(h), p, static_cast<const char*>(dact),
+                                                          static_cast<char*>(dh), dp, n_rows_ptr, max_rows, F, kind);
+  return 0;
+}
+
 }  // namespace b200ep

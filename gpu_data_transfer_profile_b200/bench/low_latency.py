@@ -35,6 +35,9 @@ def main() -> int:
                     help="launch the kernels with programmatic stream serialisation (launch latencies overlap)")
     ap.add_argument("--signal-mode", type=int, choices=(0, 1), default=None,
                     help="0: every send CTA signals every peer; 1: the last CTA does; default: by group size")
+    ap.add_argument("--combine", choices=("pull", "push"), default="pull",
+                    help="pull: the expert output lies in the buffer's in-place combine input and is loaded by its "
+                         "source ranks (one kernel); push: it is sent back to per-(token, k) slots (two kernels)")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--jsonl", default=None)
     a = ap.parse_args()
@@ -71,10 +74,18 @@ def main() -> int:
         return y
 
     dispatch_only()
+    pull = a.combine == "pull"
     y_static = dequant().clone()     # timing input for combine (row order of this first dispatch)
+    if pull:
+        # the experts write their output in place: outside the timed region, as the expert GEMM's epilogue would
+        y_in = buf.get_next_low_latency_combine_buffer(state["handle"])
+        y_in.copy_(y_static)
 
     def combine_only():
-        buf.low_latency_combine(y_static if fp8 else state["recv"], idx, w, state["handle"], out=out)
+        if pull:
+            buf.low_latency_combine(y_in, idx, w, state["handle"], out=out)
+        else:
+            buf.low_latency_combine(y_static if fp8 else state["recv"], idx, w, state["handle"], out=out)
 
     def step():
         dispatch_only()
@@ -93,7 +104,11 @@ def main() -> int:
     # correctness: one more round whose expert input is built from THAT dispatch (the slot order
     # inside a (local expert, source) block is not fixed between calls)
     dispatch_only()
-    buf.low_latency_combine(dequant(), idx, w, state["handle"], out=out)
+    if pull:
+        y_in.copy_(dequant())
+        buf.low_latency_combine(y_in, idx, w, state["handle"], out=out)
+    else:
+        buf.low_latency_combine(dequant(), idx, w, state["handle"], out=out)
     buf.check_status()
     tol = 0.6 if fp8 else 0.08
     ok = torch.allclose(out.float(), x.float() * w.sum(1, keepdim=True), atol=tol, rtol=0.08)
@@ -101,9 +116,10 @@ def main() -> int:
     send_c = T * K * H * 2
     D.ordered_print(f"[rank {rank}] low-latency dispatch+combine eager={eager['mean_ms'] * 1e3:.1f} us "
                     f"dispatch={d_only['mean_ms'] * 1e3:.1f} us combine={c_only['mean_ms'] * 1e3:.1f} us "
-                    f"graph={graphed['mean_ms'] * 1e3:.1f} us (min {graphed['min_ms'] * 1e3:.1f} us) check={'OK' if ok else 'FAIL'}")
+                    f"graph={graphed['mean_ms'] * 1e3:.1f} us (min {graphed['min_ms'] * 1e3:.1f} us) combine={a.combine} "
+                    f"check={'OK' if ok else 'FAIL'}")
     all_ok = D.all_ranks_boolean(ok)
-    C.emit(rank, dict(bench="low_latency", ep=a.ep, tokens=T, hidden=H, experts=E, topk=K, fp8=fp8,
+    C.emit(rank, dict(bench="low_latency", combine=a.combine, ep=a.ep, tokens=T, hidden=H, experts=E, topk=K, fp8=fp8,
                       eager_us_max_over_ranks=eager["max_over_ranks_ms"] * 1e3,
                       graph_us_max_over_ranks=graphed["max_over_ranks_ms"] * 1e3,
                       dispatch_us_max_over_ranks=d_only["max_over_ranks_ms"] * 1e3,

@@ -6,37 +6,15 @@ Tile scheduling reads the per-expert row offsets on the device. Backward (SwiGLU
 data gradients run on the same grouped GEMM reading the forward weights in place as an N-major
 operand, the two weight gradients on the ragged-reduction kernel (`ops.gemm.grouped_wgrad`), the
 element-wise part on the fused SwiGLU backward kernel; no library GEMM and no host-side split.
-Other activations fall back to autograd over per-expert library GEMMs.
+gelu / silu / relu (`DeepEP_Megatron/test_deepep_moe_dispatch_combine.py:516-526`) take the same
+route with the ungated activation kernels of csrc/gemm/swiglu.cu.
 """
 from __future__ import annotations
 
 import torch
-import torch.nn.functional as F
 
 from ..ops import gemm as G
-from .experts import GroupedExpertsBase, activate
-
-
-def _mlp_backward(x, w1, w2, probs, counts, dy, gated, activation):
-    """Per-expert backward of y = fc2(act(fc1(x)) * p). Returns (dx, dw1, dw2, dprobs)."""
-    dx = torch.empty_like(x)
-    dw1, dw2 = torch.zeros_like(w1), torch.zeros_like(w2)
-    dp = torch.zeros_like(probs)
-    r = 0
-    for e, c in enumerate(counts):
-        if c == 0:
-            continue
-        sl = slice(r, r + c)
-        with torch.enable_grad():
-            xe = x[sl].detach().requires_grad_(True)
-            w1e, w2e = w1[e].detach().requires_grad_(True), w2[e].detach().requires_grad_(True)
-            pe = probs[sl].detach().requires_grad_(True)
-            a = activate(F.linear(xe, w1e), activation)
-            y = F.linear((a * pe[:, None]).to(xe.dtype), w2e)
-        gx, g1, g2, gp = torch.autograd.grad(y, [xe, w1e, w2e, pe], dy[sl])
-        dx[sl], dw1[e], dw2[e], dp[sl] = gx, g1, g2, gp
-        r += c
-    return dx, dw1, dw2, dp
+from .experts import GroupedExpertsBase
 
 
 def _wgrad(dy, a, counts, out_shape, expert_off=None):
@@ -71,21 +49,20 @@ class _GroupedMLP(torch.autograd.Function):
             ctx.save_for_backward(x, w1, w2, probs, h, act)
             return y
         h = G.grouped_gemm(x, w1, expert_off)
-        act = (activate(h, activation) * probs[:, None]).to(x.dtype)
-        ctx.save_for_backward(x, w1, w2, probs)
+        act = G.act_fwd(h, probs, activation)
+        ctx.save_for_backward(x, w1, w2, probs, h, act)
         return G.grouped_gemm(act, w2, expert_off)
 
     @staticmethod
     def backward(ctx, dy):
         dy = dy.contiguous()
-        if ctx.activation != "swiglu":
-            x, w1, w2, probs = ctx.saved_tensors
-            dx, dw1, dw2, dp = _mlp_backward(x, w1, w2, probs, ctx.counts, dy, False, ctx.activation)
-            return dx, dw1, dw2, dp, None, None, None
         x, w1, w2, probs, h, act = ctx.saved_tensors
         rows = sum(ctx.counts)
         dact = G.grouped_gemm(dy, w2, ctx.off, w_kn=True)                             # [rows, F]
-        dh, dp = G.swiglu_bwd(h, probs, dact)
+        if ctx.activation == "swiglu":
+            dh, dp = G.swiglu_bwd(h, probs, dact)
+        else:
+            dh, dp = G.act_bwd(h, probs, dact, ctx.activation)
         dx = G.grouped_gemm(dh, w1, ctx.off, w_kn=True)                               # [rows, H]
         dw2 = _wgrad(dy[:rows], act[:rows], ctx.counts, w2.shape, ctx.off)
         dw1 = _wgrad(dh[:rows], x[:rows], ctx.counts, w1.shape, ctx.off)
@@ -121,13 +98,45 @@ class _GroupedMLPFusedCombine(torch.autograd.Function):
 
 
 class Tcgen05GroupedExperts(GroupedExpertsBase):
+    """`use_fp8=True` adds an inference path for inputs that arrive as (e4m3 rows, 1x128 f32 scales),
+    i.e. the output of an fp8 dispatch: fc1 runs on the block-scaled fp8 tensor-core kernel against
+    fp8 copies of the fc1 weights (one scale per 128 x 128 block, refreshed by `refresh_fp8_weights`),
+    SwiGLU x prob in its epilogue; fc2 stays bf16. Parameters and training stay bf16."""
+
     def __init__(self, num_local_experts, hidden_size, ffn_hidden_size, dtype=torch.bfloat16,
-                 activation="swiglu", device="cuda", init_std: float = 0.02):
+                 activation="swiglu", device="cuda", init_std: float = 0.02, use_fp8: bool = False):
         if dtype != torch.bfloat16:
-            raise ValueError("the tcgen05 grouped GEMM takes bf16 operands")
+            raise ValueError("the tcgen05 grouped GEMM takes bf16 parameters (fp8 inputs: use_fp8=True)")
         if hidden_size % 8 or ffn_hidden_size % 8 or (activation == "swiglu" and ffn_hidden_size % 128):
             raise ValueError("hidden/ffn sizes must be multiples of 8 (ffn of 128 with swiglu)")
+        if use_fp8 and (hidden_size % 128 or ffn_hidden_size % 128):
+            raise ValueError("the fp8 path needs hidden and ffn sizes that are multiples of 128")
         super().__init__(num_local_experts, hidden_size, ffn_hidden_size, dtype, activation, device, init_std)
+        self.use_fp8 = bool(use_fp8)
+        self._w1_fp8 = None
+
+    @torch.no_grad()
+    def refresh_fp8_weights(self) -> None:
+        """Re-quantise the fc1 weights (call after the bf16 parameters changed)."""
+        self._w1_fp8 = G.quantize_weights_128x128(self.weight1)
+
+    @torch.no_grad()
+    def forward_fp8(self, hidden_states, tokens_per_expert, routed_probs, expert_off=None):
+        """hidden_states = (e4m3 [rows, H], f32 [rows, H/128]) as delivered by an fp8 dispatch.
+        Forward only. Returns bf16 [rows, H]."""
+        if not self.use_fp8:
+            raise ValueError("construct the experts with use_fp8=True")
+        x_q, x_s = hidden_states
+        if self._w1_fp8 is None:
+            self.refresh_fp8_weights()
+        w_q, w_s = self._w1_fp8
+        counts, off = self._offsets(tokens_per_expert, x_q.device, expert_off)
+        probs = routed_probs.float().contiguous()
+        if self.activation == "swiglu":
+            act = G.grouped_gemm_fp8(x_q, x_s, w_q, w_s, off, swiglu=True, row_prob=probs)
+        else:
+            act = G.act_fwd(G.grouped_gemm_fp8(x_q, x_s, w_q, w_s, off), probs, self.activation)
+        return G.grouped_gemm(act, self.weight2, off)
 
     @staticmethod
     def _offsets(tokens_per_expert, device, expert_off=None):
@@ -137,6 +146,8 @@ class Tcgen05GroupedExperts(GroupedExpertsBase):
         return counts, expert_off
 
     def forward(self, hidden_states, tokens_per_expert, routed_probs, expert_off=None):
+        if isinstance(hidden_states, tuple):
+            return self.forward_fp8(hidden_states, tokens_per_expert, routed_probs, expert_off)
         counts, off = self._offsets(tokens_per_expert, hidden_states.device, expert_off)
         return _GroupedMLP.apply(hidden_states.contiguous(), self.weight1, self.weight2,
                                  routed_probs.float().contiguous(), off, counts, self.activation)
@@ -161,6 +172,5 @@ class Tcgen05GroupedExperts(GroupedExpertsBase):
         if self.activation == "swiglu":
             act = G.grouped_gemm_swiglu(x, self.weight1, off, routed_probs.float().contiguous())
         else:
-            act = (activate(G.grouped_gemm(x, self.weight1, off), self.activation)
-                   * routed_probs.float()[:, None]).to(x.dtype)
+            act = G.act_fwd(G.grouped_gemm(x, self.weight1, off), routed_probs.float().contiguous(), self.activation)
         return buffer.fused_fc2_combine(act, self.weight2, handle)

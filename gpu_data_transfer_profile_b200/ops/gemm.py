@@ -109,3 +109,62 @@ def swiglu_bwd(h: torch.Tensor, row_prob: Optional[torch.Tensor], dact: torch.Te
     dp = torch.empty(h.shape[0], dtype=torch.float32, device=h.device)
     _ext.load().swiglu_bwd(h, row_prob, dact.contiguous(), dh, dp)
     return dh, dp
+
+
+ACT_KIND = {"gelu": 0, "silu": 1, "relu": 2}
+
+
+def act_fwd(h: torch.Tensor, row_prob: Optional[torch.Tensor], activation: str) -> torch.Tensor:
+    """act = f(h) * row_prob[:, None] for f in gelu (erf form) / silu / relu (bf16 in, bf16 out)."""
+    act = torch.empty_like(h)
+    _ext.load().act_fwd(h, row_prob, act, ACT_KIND[activation])
+    return act
+
+
+def act_bwd(h: torch.Tensor, row_prob: Optional[torch.Tensor], dact: torch.Tensor, activation: str):
+    """-> (dh bf16 [rows, F], dprob f32 [rows]) for act = f(h) * prob."""
+    dh = torch.empty_like(h)
+    dp = torch.empty(h.shape[0], dtype=torch.float32, device=h.device)
+    _ext.load().act_bwd(h, row_prob, dact.contiguous(), dh, dp, ACT_KIND[activation])
+    return dh, dp
+
+
+# ---- block-scaled fp8 (e4m3) forward path ---------------------------------------------------------
+def quantize_rows_1x128(x: torch.Tensor):
+    """bf16/f32 [rows, K] -> (e4m3 [rows, K], f32 scales [rows, K/128]); scale = max(amax, 1e-4) / 448
+    per row and 128 channels: the same rule as the cast inside the fp8 dispatch kernel."""
+    rows, K = x.shape
+    xf = x.float().view(rows, K // 128, 128)
+    amax = xf.abs().amax(-1).clamp_min(1e-4)
+    q = (xf * (448.0 / amax)[..., None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(rows, K)
+    return q, (amax / 448.0).contiguous()
+
+
+def quantize_weights_128x128(w: torch.Tensor):
+    """[E, N, K] -> (e4m3 [E, N, K], f32 scales [E, N/128, K/128]), one scale per 128 x 128 block."""
+    E, N, K = w.shape
+    wf = w.float().view(E, N // 128, 128, K // 128, 128)
+    amax = wf.abs().amax(dim=(2, 4)).clamp_min(1e-6)
+    q = (wf * (448.0 / amax)[:, :, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(E, N, K)
+    return q.contiguous(), (amax / 448.0).contiguous()
+
+
+def dequantize_weights_128x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    E, N, K = q.shape
+    return (q.float().view(E, N // 128, 128, K // 128, 128) * s[:, :, None, :, None]).view(E, N, K)
+
+
+def grouped_gemm_fp8(a_q: torch.Tensor, a_s: torch.Tensor, w_q: torch.Tensor, w_s: torch.Tensor,
+                     expert_off: torch.Tensor, *, swiglu: bool = False, row_prob: Optional[torch.Tensor] = None,
+                     out: Optional[torch.Tensor] = None, ctas: int = 0, band_bytes: Optional[int] = None) -> torch.Tensor:
+    """Block-scaled fp8 grouped GEMM on the tensor cores (`tcgen05.mma kind::f8f6f4`, partial sums
+    promoted to f32 per 128-wide reduction block with the product of both scales).
+    a_q e4m3 [rows, K] + a_s f32 [rows, K/128] (what the fp8 dispatch delivers), w_q e4m3 [E, Nw, K]
+    + w_s f32 [E, Nw/128, K/128]. Plain: out[r] = a[r] @ w[e(r)].T -> bf16 [rows, Nw]. swiglu: Nw = 2F
+    (gate rows first), out = silu(gate) * linear * row_prob -> bf16 [rows, F]."""
+    n_out = w_q.shape[1] // 2 if swiglu else w_q.shape[1]
+    if out is None:
+        out = torch.empty((a_q.shape[0], n_out), dtype=torch.bfloat16, device=a_q.device)
+    _ext.load().grouped_gemm_fp8(a_q, a_s, w_q, w_s, expert_off, SWIGLU if swiglu else PLAIN, out, row_prob, 0,
+                                 ctas or _ctas(a_q.device), max(256, (band_bytes or BAND_BYTES) // a_q.shape[1] // 256 * 256))
+    return out

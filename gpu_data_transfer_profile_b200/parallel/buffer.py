@@ -71,9 +71,6 @@ class DispatchHandle:
     num_recv_tokens_per_expert_list: List[int] = field(default_factory=list)
     fp8: bool = False
     recv_prob: Optional[torch.Tensor] = None
-    bnd: Optional[torch.Tensor] = None     # [R, BND_STRIDE] first receive row of (source, token chunk); rank mode
-    nch: int = 0                           # combine chunks per rank used by this dispatch
-    chunk_tokens: int = 32                 # tokens per combine chunk on THIS rank
     carve_key: tuple = ()                  # region layout that the rows / slots refer to
     cap: int = 0                           # receive capacity (rows) of that layout
 
@@ -87,7 +84,7 @@ class _Carve:
 
     The control area starts with the blocks whose position must never depend on the shape (flag
     words are epochs that only grow, so a word must not be reused for anything else): channel
-    flags, per-chunk combine flags, chunk-boundary tables. The count matrices follow."""
+    flags and the pull-combine announcements. The count matrices follow."""
 
     def __init__(self, nbytes: int, R: int, E: int, K: int, H: int, row_bytes: int, comb_row_bytes: int,
                  max_recv_rows: int = 0):
@@ -95,11 +92,8 @@ class _Carve:
         self.key = (E, K, H, row_bytes, comb_row_bytes)
         self.flags = 0
         off = align_up(C.NUM_CHANNELS * C.MAX_RANKS * 4, REGION_ALIGN)
-        self.chunk_flags = off
-        off = align_up(off + C.MAX_RANKS * C.MAX_COMB_CHUNKS * 4, REGION_ALIGN)
-        bsz = align_up(C.MAX_RANKS * C.BND_STRIDE * 4, REGION_ALIGN)
-        self.recv_bnd = (off, off + bsz)
-        off += 2 * bsz
+        self.pull_info = off
+        off = align_up(off + C.MAX_RANKS * 4 * 8, REGION_ALIGN)
         csz = align_up(R * (R + E) * 4, REGION_ALIGN)
         self.counts = (off, off + csz)
         off += 2 * csz
@@ -134,7 +128,7 @@ class _Carve:
             d, c = self.regions[dispatch_parity], self.regions[combine_parity]
             out = [self.flags, self.counts[notify_parity], d["recv_x"], d["recv_scales"],
                    d["recv_topk_idx"], d["recv_topk_w"], d["recv_meta"], d["recv_prob"],
-                   c["comb_x"], c["comb_w"], self.chunk_flags, self.recv_bnd[dispatch_parity]]
+                   c["comb_x"], c["comb_w"], self.pull_info]
             self._lists[key] = out
         return out
 
@@ -162,9 +156,12 @@ def _nvtx(name):
 
 class Buffer:
     num_sms: int = 24
-    # Combine chunks per rank (0 = one flag per rank when the whole send is done). Must be the same
-    # on every rank of the group. The source reduces chunk c while chunk c+1 is still arriving.
-    combine_chunks: int = 16
+    # How combine moves the rows. "push": every rank stores its rows into slots on the source,
+    # which then reduces the slots. "pull": the rows stay where they are and the source LOADS and
+    # reduces them in one pass; possible when the rows (and the side values, if any) lie inside
+    # the symmetric region, e.g. the zero-copy output of dispatch or `combine_input()`.
+    # "auto" pulls whenever that is the case. Every rank of the group must take the same path.
+    combine_transport: str = "auto"
 
     # ---- static configuration --------------------------------------------------------
     @staticmethod
@@ -214,11 +211,9 @@ class Buffer:
             self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
             self.status.view(torch.int64)[1] = self.host_word + 4 * _STATUS_MIRROR_SLOT
             self.counters = torch.zeros(8, dtype=torch.int32, device=self.device)
-            self._comb_scratch = torch.zeros(self.C.MAX_RANKS * self.C.MAX_COMB_CHUNKS + 2,
-                                             dtype=torch.int32, device=self.device)
             self._side_stream = (torch.cuda.current_stream() if self.world.local
                                  else torch.cuda.Stream(device=self.device))
-            self.comm_stream = torch.cuda.current_stream()
+            self.comm_stream = None
         self._async_outstanding = False
         # One launch may both send and wait for peers only when no other rank shares this GPU.
         self._single_launch = (not self.world.local) or self.group_size == 1
@@ -262,7 +257,6 @@ class Buffer:
     def _clear_status(self) -> None:
         self.status[0:2].zero_()
         self.counters.zero_()
-        self._comb_scratch.zero_()
         self.C.host_write_i32(self.host_word, _STATUS_MIRROR_SLOT, 0)
 
     @staticmethod
@@ -297,43 +291,34 @@ class Buffer:
                                  self.num_max_recv_tokens)
         return self._carve
 
-    def _chunks(self, T: int):
-        """(nch, tokens per chunk) of this rank's combine chunks: nch is the same on every rank,
-        the chunk length depends on this rank's token count (a multiple of 32)."""
-        nch = max(0, min(int(Buffer.combine_chunks), self.C.MAX_COMB_CHUNKS))
-        if nch == 0:
-            return 0, self.C.CHUNK_TOKENS
-        c32 = max((T + self.C.CHUNK_TOKENS - 1) // self.C.CHUNK_TOKENS, 1)
-        return nch, ((c32 + nch - 1) // nch) * self.C.CHUNK_TOKENS
-
-    def _geom(self, *, E, K, T, mode, H, cap, slot_cap, epoch, epoch_wait=0, nch=0, chunk_tokens=32,
-              tail_wait=0) -> List[int]:
+    def _geom(self, *, E, K, T, mode, H, cap, slot_cap, epoch, epoch_wait=0, tail_wait=0) -> List[int]:
         R = self.group_size
         J, B = (R, R) if mode == 0 else (K, E)
-        return [self.rank, R, E, E // R, K, T, mode, J, B, H, cap, slot_cap, epoch, epoch_wait, nch,
-                chunk_tokens, tail_wait, self._timeout_ns()]
+        return [self.rank, R, E, E // R, K, T, mode, J, B, H, cap, slot_cap, epoch, epoch_wait, tail_wait,
+                self._timeout_ns()]
 
     def _meta_ints(self, E: int, mode: int, K: int) -> int:
         R = self.group_size
         El = E // R
         B = R if mode == 0 else E
-        return 2 + El + (El + 1) + (R + 1) + 2 * B + R * self.C.BND_STRIDE
+        return 2 + El + (El + 1) + (R + 1) + 2 * B
 
     def _enter(self, previous_event, allocate_on_comm_stream, async_finish):
-        """Pick the stream for this op. Synchronous calls run on the caller's stream (no stream
-        switch, no extra event traffic); `async_finish=True` or a `previous_event` uses the
-        buffer's own communication stream."""
+        """Pick the stream for this op. Synchronous calls run on the caller's stream: no stream
+        object is even looked up (`comm_stream` is None, and `torch.cuda.stream(None)` is a no-op
+        context); `async_finish=True` or a `previous_event` uses the buffer's own communication
+        stream."""
         if allocate_on_comm_stream and not async_finish:
             raise ValueError("allocate_on_comm_stream=True requires async_finish=True")
         self._poll_status()
-        compute = torch.cuda.current_stream(self.device)
         use_side = (async_finish or previous_event is not None) and not self.world.local
         if not use_side:
+            self.comm_stream = None
             if self._async_outstanding:
-                compute.wait_stream(self._side_stream)     # earlier async work on this buffer
+                torch.cuda.current_stream(self.device).wait_stream(self._side_stream)   # earlier async work
                 self._async_outstanding = False
-            self.comm_stream = compute
-            return compute
+            return None
+        compute = torch.cuda.current_stream(self.device)
         self.comm_stream = self._side_stream
         ev = getattr(getattr(previous_event, "event", None), "event", None)
         if ev is not None:
@@ -343,8 +328,8 @@ class Buffer:
         return compute
 
     def _exit(self, compute, async_finish, tensors) -> Optional[EventOverlap]:
-        if self.comm_stream == compute:
-            return EventOverlap(EventHandle(compute)) if async_finish else None
+        if compute is None:
+            return EventOverlap(EventHandle()) if async_finish else None
         for t in tensors:
             if isinstance(t, torch.Tensor) and t.is_cuda:
                 t.record_stream(compute)
@@ -468,11 +453,9 @@ class Buffer:
                                  "width as the handle's own dispatch")
             st["meta"] = handle.meta
             st["send_row"], st["send_slot"] = handle.send_row, handle.send_slot
-            st["nch"], st["chunk_tokens"] = handle.nch, handle.chunk_tokens
             return st
         self._epoch["notify"] += 1
         st["epoch_n"] = self._epoch["notify"]
-        st["nch"], st["chunk_tokens"] = self._chunks(T)
         dev = self.device
         C_chunks = max((T + self.C.CHUNK_TOKENS - 1) // self.C.CHUNK_TOKENS, 1)
         key = (max(T, 1), J, C_chunks, B)
@@ -513,7 +496,6 @@ class Buffer:
         st["regions"] = regions
         geom = self._geom(E=st["E"], K=st["K"], T=st["T"], mode=st["mode"], H=st["H"], cap=carve.cap,
                           slot_cap=carve.slot_cap, epoch=st["epoch_d"], epoch_wait=st.get("epoch_n", 0),
-                          nch=st["nch"], chunk_tokens=st["chunk_tokens"],
                           tail_wait=1 if self._single_launch else 0)
         st["geom"] = geom
         self.C.dispatch_send(geom, regions, self.peers, st["meta"], st["x"], st["fp8"], st["cached"],
@@ -527,8 +509,8 @@ class Buffer:
         El = E // R
         carve = st["carve"]
         if not self._single_launch:
-            self.C.dispatch_wait(st["geom"], st["regions"], self.region.local_ptr, st["meta"], st["cached"],
-                                 self.status_ptr)
+            self.C.wait_flags(self.region.local_ptr, 0, 1, R, st["epoch_d"], self._timeout_ns(),
+                              self.status_ptr, 2)
         if st["cached"]:
             h = st["handle"]
             n_recv, per_expert_list = h.n_recv, h.num_recv_tokens_per_expert_list
@@ -572,14 +554,9 @@ class Buffer:
         if st["mode"] == 1:
             recv_prob = keep(self.region.view(reg["recv_prob"], (n_recv,), "float32"))
         recv_meta = keep(self.region.view(reg["recv_meta"], (n_recv, 2), "int32"))
-        n_meta = st["meta"].numel()
-        bnd = None
-        if st["mode"] == 0 and st["nch"] > 0:
-            bnd = st["meta"][n_meta - R * self.C.BND_STRIDE:].view(R, self.C.BND_STRIDE)
         handle = DispatchHandle(st["mode"], st["T"], H, K, E, n_recv, st["send_row"], st["send_slot"],
                                 st["meta"], recv_meta, st["topk_idx"], st.get("is_token_in_rank"),
-                                per_expert_list, st["fp8_out"], recv_prob, bnd, st["nch"], st["chunk_tokens"],
-                                carve.key, carve.cap)
+                                per_expert_list, st["fp8_out"], recv_prob, carve.key, carve.cap)
         return recv_x, recv_topk_idx, recv_topk_w, per_expert_list, handle
 
     @_nvtx("b200ep.dispatch")
@@ -633,14 +610,11 @@ class Buffer:
         self._epoch["combine"] += 1
         ep = self._epoch["combine"]
         regions = carve.region_list(0, 0, ep & 1)
-        by_chunk = handle.bnd is not None and handle.nch > 0
         geom = self._geom(E=handle.E, K=handle.K, T=handle.T, mode=handle.mode, H=handle.H,
-                          cap=handle.n_recv, slot_cap=carve.slot_cap, epoch=ep,
-                          nch=handle.nch if by_chunk else 0, chunk_tokens=handle.chunk_tokens)
+                          cap=handle.n_recv, slot_cap=carve.slot_cap, epoch=ep)
         if topk_weights is not None:
             topk_weights = topk_weights.to(torch.float32).contiguous()
-        return dict(ep=ep, regions=regions, geom=geom, dtype=x.dtype, topk_w=topk_weights, x=x,
-                    wait_mode=2 if by_chunk else 1)
+        return dict(ep=ep, regions=regions, geom=geom, dtype=x.dtype, topk_w=topk_weights, x=x)
 
     def _combine_outputs(self, st, handle: DispatchHandle):
         out = torch.empty((handle.T, handle.H), dtype=st["dtype"], device=self.device)
@@ -649,33 +623,87 @@ class Buffer:
         return out, out_w
 
     def _combine_p1(self, x, handle: DispatchHandle, topk_weights):
-        """Send half as its own launch (several virtual ranks on one GPU)."""
+        """Push form, send half as its own launch (several virtual ranks on one GPU)."""
         st = self._combine_prepare(x, handle, topk_weights)
-        self.C.combine(st["geom"], st["regions"], self.peers, 1, 0, self._blocks(), 0,
-                       handle.n_recv_dev, handle.recv_meta, x, st["topk_w"],
-                       handle.bnd if st["wait_mode"] == 2 else None, self._comb_scratch,
+        self.C.combine(st["geom"], st["regions"], self.peers, 1, max(1, Buffer.num_sms), False,
+                       handle.n_recv_dev, handle.recv_meta, x, st["topk_w"], self.counters[2:3],
                        None, None, None, None, self.status_ptr)
         return st
 
     def _combine_p2(self, st, handle: DispatchHandle, weights=None):
-        """Reduce half as its own launch."""
+        """Push form, reduce half as its own launch (waits for every rank's combine flag first)."""
         out, out_w = self._combine_outputs(st, handle)
-        self.C.combine(st["geom"], st["regions"], self.peers, 2, 0, self._blocks() * 2, st["wait_mode"],
-                       None, None, None, None, None, self._comb_scratch,
+        self.C.combine(st["geom"], st["regions"], self.peers, 2, max(1, Buffer.num_sms), True,
+                       None, None, None, None, self.counters[2:3],
                        handle.send_slot, weights, out, out_w, self.status_ptr)
         return out, out_w
 
     def _combine_fused(self, x, handle: DispatchHandle, topk_weights, weights=None):
-        """Both halves in ONE launch: the first `n_send` CTAs to start send, the others reduce each
-        token chunk as soon as every rank has returned it."""
+        """Push form in ONE launch: every CTA sends its share of the rows, then waits for the peers'
+        flags and reduces its share of the tokens."""
         st = self._combine_prepare(x, handle, topk_weights)
         out, out_w = self._combine_outputs(st, handle)
-        n_send = max(1, Buffer.num_sms)
-        self.C.combine(st["geom"], st["regions"], self.peers, 0, n_send, 2 * n_send, st["wait_mode"],
-                       handle.n_recv_dev, handle.recv_meta, x, st["topk_w"],
-                       handle.bnd if st["wait_mode"] == 2 else None, self._comb_scratch,
+        self.C.combine(st["geom"], st["regions"], self.peers, 0, max(1, Buffer.num_sms), True,
+                       handle.n_recv_dev, handle.recv_meta, x, st["topk_w"], self.counters[2:3],
                        handle.send_slot, weights, out, out_w, self.status_ptr)
         return out, out_w
+
+    def _region_offset(self, t: Optional[torch.Tensor]) -> int:
+        """Byte offset of tensor `t` inside this rank's symmetric region, or -1 if it lies elsewhere."""
+        if t is None or not t.is_cuda or not t.is_contiguous():
+            return -1
+        lo = self.region.local_ptr
+        p = t.data_ptr()
+        if p < lo or p + t.numel() * t.element_size() > lo + self.num_nvl_bytes:
+            return -1
+        return p - lo
+
+    def _use_pull(self, x, topk_weights) -> bool:
+        mode = Buffer.combine_transport
+        if mode == "push":
+            return False
+        ok = self._region_offset(x) >= 0 and x.data_ptr() % 16 == 0 and (
+            topk_weights is None or (topk_weights.dtype == torch.float32 and self._region_offset(topk_weights) >= 0))
+        if mode == "pull" and not ok:
+            raise ValueError("combine_transport='pull' needs x (and topk_weights) inside the symmetric region")
+        return ok
+
+    def _combine_pull(self, phase: int, x, handle: DispatchHandle, topk_weights, weights=None, out=None):
+        """phase 0: announce + wait + reduce in one launch; 1: announce only; 2: wait + reduce."""
+        carve = self._carve
+        if carve is None or carve.key[:3] != (handle.E, handle.K, handle.H):
+            raise ValueError("combine must follow a dispatch of the same shape on this buffer")
+        if x.dim() != 2 or x.shape[1] != handle.H or x.dtype not in _ELEM_DTYPE:
+            raise ValueError("x must be a [num_recv_tokens, hidden] bf16/fp16/fp32 tensor")
+        if phase != 2:
+            self._epoch["combine"] += 1
+        ep = self._epoch["combine"]
+        regions = carve.region_list(0, 0, ep & 1)
+        geom = self._geom(E=handle.E, K=handle.K, T=handle.T, mode=handle.mode, H=handle.H,
+                          cap=carve.cap, slot_cap=carve.slot_cap, epoch=ep)
+        if out is None:
+            out = torch.empty((handle.T, handle.H), dtype=x.dtype, device=self.device)
+        out_w = (torch.empty((handle.T, handle.K), dtype=torch.float32, device=self.device)
+                 if topk_weights is not None else None)
+        self.C.combine_pull(geom, regions, self.peers, phase, max(1, Buffer.num_sms),
+                            self._region_offset(x), self._region_offset(topk_weights), int(x.shape[0]),
+                            handle.send_row, handle.topk_idx if handle.mode == 1 else None, weights, out, out_w,
+                            self.status_ptr)
+        return out, out_w
+
+    def combine_input(self, num_rows: int, hidden: int, dtype=torch.bfloat16) -> torch.Tensor:
+        """A [num_rows, hidden] tensor INSIDE the symmetric region for the expert computation to
+        write its result into, so that combine can pull it without a copy. It aliases the combine
+        slot area of the next combine's parity: valid until that combine returns, and only for
+        callers that then combine this very tensor."""
+        carve = self._carve
+        if carve is None:
+            raise ValueError("combine_input() must follow a dispatch on this buffer")
+        es = torch.empty((), dtype=dtype).element_size()
+        if num_rows * hidden * es > carve.slot_cap * carve.key[4]:
+            raise ValueError("combine_input larger than the combine area of this buffer")
+        off = carve.regions[(self._epoch["combine"] + 1) & 1]["comb_x"]
+        return self.region.view(off, (num_rows, hidden), _ELEM_DTYPE[dtype])
 
     @_nvtx("b200ep.combine")
     def combine(self, x, handle: DispatchHandle, topk_weights=None, bias=None,
@@ -691,8 +719,16 @@ class Buffer:
         `item_weights[T,J]` (J = ranks in rank mode, top-k in expert mode) turns it into a
         weighted reduction applied on arrival."""
         compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
+        if topk_weights is not None and topk_weights.dtype != torch.float32:
+            topk_weights = topk_weights.to(torch.float32)
         with torch.cuda.stream(self.comm_stream):
-            if self._single_launch:
+            if self._use_pull(x, topk_weights):
+                if self._single_launch:
+                    out, out_w = self._combine_pull(0, x, handle, topk_weights, item_weights)
+                else:
+                    self._combine_pull(1, x, handle, topk_weights)
+                    out, out_w = self._combine_pull(2, x, handle, topk_weights, item_weights)
+            elif self._single_launch:
                 out, out_w = self._combine_fused(x, handle, topk_weights, item_weights)
             else:
                 st = self._combine_p1(x, handle, topk_weights)
@@ -745,9 +781,10 @@ class Buffer:
             if self._ll_words is None:
                 # device-resident op state (epochs and arrival targets); lives as long as the buffer
                 # because the peers' arrival counters are cumulative
-                self._ll_words = torch.zeros(12, dtype=torch.int32, device=dev)
+                self._ll_words = torch.zeros(18, dtype=torch.int32, device=dev)
             self._ll = dict(key=key, carve=carve, words=self._ll_words,
-                            send_cnt=torch.zeros(2 * E, dtype=torch.int32, device=dev))
+                            send_cnt=torch.zeros(2 * E, dtype=torch.int32, device=dev),
+                            send_slot=torch.full((M * K,), -1, dtype=torch.int32, device=dev))
             self._carve = None
         return self._ll
 
@@ -759,7 +796,7 @@ class Buffer:
         return [self.rank, R, E, El, K, H, M, T, int(fp8), 0, *c.count, *c.recv_x, *c.recv_scales,
                 *c.recv_src, *c.comb_x, self._timeout_ns(), *c.recv_tag, min(M, 128), El * Buffer.LL_SPLIT,
                 (1 if R >= 8 else 0) if Buffer.ll_signal_mode is None else int(Buffer.ll_signal_mode),
-                int(bool(Buffer.ll_overlap_launches))]
+                int(bool(Buffer.ll_overlap_launches)), c.comb_in, *c.range_tab]
 
     def _ll_dispatch_send(self, x, topk_idx, M, E, use_fp8):
         if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
@@ -773,7 +810,8 @@ class Buffer:
         K = topk_idx.shape[1]
         st = self._ll_state(E, K, H, M)
         pv = self._ll_params(st, T, use_fp8)
-        self.C.ll_dispatch_send(pv, self.peers, x, topk_idx, st["send_cnt"], st["words"][0:6], self.status_ptr)
+        self.C.ll_dispatch_send(pv, self.peers, x, topk_idx, st["send_cnt"], st["words"][0:6], self.status_ptr,
+                                st["send_slot"])
         return dict(st=st, pv=pv, T=T, H=H, K=K, E=E, M=M, fp8=use_fp8, topk_idx=topk_idx, x=x)
 
     def _ll_dispatch_recv(self, d):
@@ -819,6 +857,35 @@ class Buffer:
         ev = self._exit(compute, async_finish, flat + [count, x])
         return recv_x, count, handle, ev, None
 
+    def get_next_low_latency_combine_buffer(self, handle) -> torch.Tensor:
+        """bf16 [E_local, R*M, hidden] INSIDE the symmetric region, row (e, j) matching row (e, j) of
+        the `recv_x` that `low_latency_dispatch` returned with this handle. Experts that write their
+        output here let `low_latency_combine` pull the rows in place (one kernel, no send half).
+        The tensor has a fixed address (usable under CUDA-graph replay) and may be rewritten once
+        the next `low_latency_dispatch` on this buffer has returned."""
+        _src, _range, M, H, E, _count, K = handle
+        st = self._ll_state(E, K, H, M)
+        El = E // self.group_size
+        return self.region.view(st["carve"].comb_in, (El, self.group_size * M, H), "bfloat16")
+
+    def _ll_combine_pull(self, phase: int, topk_idx, topk_weights, handle, out=None):
+        _src, rng, M, H, E, _count, K = handle
+        st = self._ll_state(E, K, H, M)
+        topk_idx = topk_idx.to(torch.int64).contiguous()
+        T = topk_idx.shape[0]
+        pv = self._ll_params(st, T, False)
+        if out is None:
+            out = torch.empty((T, H), dtype=torch.bfloat16, device=self.device)
+        w = topk_weights.to(torch.float32).contiguous() if topk_weights is not None else None
+        self.C.ll_combine_pull(pv, self.peers, phase, rng, st["send_slot"], topk_idx, w, out,
+                               st["words"][12:18], self.status_ptr)
+        return out
+
+    def _ll_is_combine_buffer(self, x, handle) -> bool:
+        if self._ll is None:
+            return False
+        return x.data_ptr() == self.region.local_ptr + self._ll["carve"].comb_in
+
     def _ll_combine_send(self, x, handle):
         src_info, _range, M, H, E, count, K = handle
         st = self._ll_state(E, K, H, M)
@@ -841,9 +908,21 @@ class Buffer:
 
     @_nvtx("b200ep.ll_combine")
     def low_latency_combine(self, x, topk_idx, topk_weights, handle, async_finish: bool = False,
-                            return_recv_hook: bool = False, out: Optional[torch.Tensor] = None):
-        """-> (combined_x [T,H] bf16 = sum_k topk_weights[t,k] * expert output of (t,k), event, hook)."""
+                            return_recv_hook: bool = False, out: Optional[torch.Tensor] = None,
+                            zero_copy: bool = False):
+        """-> (combined_x [T,H] bf16 = sum_k topk_weights[t,k] * expert output of (t,k), event, hook).
+        When `x` is the tensor from `get_next_low_latency_combine_buffer` (or `zero_copy=True`, which
+        asserts that the expert output already lies there), the rows are pulled in place by one
+        kernel; otherwise they are sent back to per-(token, k) slots and reduced there. Every rank
+        of the group must use the same form."""
         compute = self._enter(None, False, False)
+        if zero_copy or self._ll_is_combine_buffer(x, handle):
+            with torch.cuda.stream(self.comm_stream):
+                res = self._ll_combine_pull(0 if self._single_launch else 1, topk_idx, topk_weights, handle, out)
+                if not self._single_launch:
+                    res = self._ll_combine_pull(2, topk_idx, topk_weights, handle, res)
+            ev = self._exit(compute, async_finish, [res])
+            return res, ev, ((lambda: res) if return_recv_hook else None)
         with torch.cuda.stream(self.comm_stream):
             c = self._ll_combine_send(x, handle)
             if return_recv_hook:
@@ -863,12 +942,13 @@ class _LLCarve:
         El = E // R
         rows = El * R * M
         return dict(recv_x=rows * H * 2, recv_scales=rows * max(H // 128, 1) * 4, recv_src=rows * 4,
-                    recv_tag=rows * 4, comb_x=M * K * H * 2)
+                    recv_tag=rows * 4, comb_x=M * K * H * 2, range_tab=R * El * 4)
 
     @staticmethod
     def required_bytes(R, E, M, H, K) -> int:
         s = _LLCarve._sizes(R, E, M, H, K)
-        return FIXED_BYTES + 2 * sum(align_up(v, REGION_ALIGN) for v in s.values()) + REGION_ALIGN
+        comb_in = align_up((E // R) * R * M * H * 2, REGION_ALIGN)      # in-place expert output, one copy
+        return FIXED_BYTES + 2 * sum(align_up(v, REGION_ALIGN) for v in s.values()) + comb_in + REGION_ALIGN
 
     def __init__(self, nbytes: int, R: int, E: int, M: int, H: int, K: int):
         need = self.required_bytes(R, E, M, H, K)
@@ -889,6 +969,7 @@ class _LLCarve:
             for name, sz in names.items():
                 getattr(self, name)[p] = off
                 off = align_up(off + sz, REGION_ALIGN)
+        self.comb_in = off          # [El][R*M][H] bf16: where the experts write when combine pulls
 
 
 def _fused_fc2_combine(self: Buffer, act: torch.Tensor, w2: torch.Tensor, handle: DispatchHandle,
@@ -920,7 +1001,7 @@ def _fused_fc2_combine(self: Buffer, act: torch.Tensor, w2: torch.Tensor, handle
         geom = self._geom(E=handle.E, K=handle.K, T=handle.T, mode=1, H=handle.H, cap=handle.n_recv,
                           slot_cap=carve.slot_cap, epoch=ep)
         # the GEMM's last CTA raises one flag per rank: the reduce launch waits for those
-        st = dict(ep=ep, regions=regions, geom=geom, dtype=torch.bfloat16, topk_w=None, wait_mode=1)
+        st = dict(ep=ep, regions=regions, geom=geom, dtype=torch.bfloat16, topk_w=None)
         out, _ = self._combine_p2(st, handle, item_weights)
     self._exit(compute, False, [out, act])
     return out

@@ -41,6 +41,14 @@ class LocalGroup:
         return [b._dispatch_p3(sts[r], zero_copy) for r, b in enumerate(self.buffers)]
 
     def combine(self, ys, handles, topk_weights=None, item_weights=None):
+        tw = lambda r: topk_weights[r] if topk_weights is not None else None
+        if all(b._use_pull(ys[r], tw(r)) for r, b in enumerate(self.buffers)):
+            # rows stay in their producers' regions: every rank announces, then every rank pulls
+            for r, b in enumerate(self.buffers):
+                b._combine_pull(1, ys[r], handles[r], tw(r))
+            return [b._combine_pull(2, ys[r], handles[r], tw(r),
+                                    item_weights[r] if item_weights is not None else None)
+                    for r, b in enumerate(self.buffers)]
         sts = [b._combine_p1(ys[r], handles[r], topk_weights[r] if topk_weights is not None else None)
                for r, b in enumerate(self.buffers)]
         return [b._combine_p2(sts[r], handles[r], item_weights[r] if item_weights is not None else None)
@@ -54,6 +62,11 @@ class LocalGroup:
         return [b._ll_dispatch_recv(ds[r]) for r, b in enumerate(self.buffers)]
 
     def low_latency_combine(self, ys, topk_idx, topk_weights, handles):
+        if all(b._ll_is_combine_buffer(ys[r], handles[r]) for r, b in enumerate(self.buffers)):
+            for r, b in enumerate(self.buffers):            # every rank announces, then every rank pulls
+                b._ll_combine_pull(1, topk_idx[r], topk_weights[r], handles[r])
+            return [b._ll_combine_pull(2, topk_idx[r], topk_weights[r], handles[r])
+                    for r, b in enumerate(self.buffers)]
         cs = [b._ll_combine_send(ys[r], handles[r]) for r, b in enumerate(self.buffers)]
         return [b._ll_combine_recv(cs[r], topk_idx[r], topk_weights[r]) for r, b in enumerate(self.buffers)]
 

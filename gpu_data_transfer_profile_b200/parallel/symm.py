@@ -32,15 +32,25 @@ class SymmetricRegion:
         self.device = world.device
         with torch.cuda.device(self.device):
             self.local_ptr = self.C.symm_alloc(self.nbytes)
+        self._views = {}
         self.peer_ptrs: List[int] = world._map_peers(self)
         self._opened = [p for i, p in enumerate(self.peer_ptrs)
                         if world.is_remote(i) and p != self.local_ptr]
 
     def view(self, offset: int, shape, dtype: str) -> torch.Tensor:
-        return self.C.view_tensor(self.local_ptr + int(offset), list(shape), dtype,
-                                  self.device.index)
+        """Tensor over region bytes. Views are cached by (offset, shape, dtype): a steady-state loop
+        asks for the same few views every step, and wrapping a pointer costs microseconds."""
+        key = (int(offset), tuple(shape), dtype)
+        t = self._views.get(key)
+        if t is None:
+            if len(self._views) > 256:
+                self._views.clear()
+            t = self.C.view_tensor(self.local_ptr + int(offset), list(shape), dtype, self.device.index)
+            self._views[key] = t
+        return t
 
     def close(self):
+        self._views = {}
         if self.local_ptr:
             for p in self._opened:
                 self.C.ipc_close(p)

@@ -171,4 +171,8 @@ def run_main(main) -> None:
         os._exit(1)
     sys.stdout.flush()
     sys.stderr.flush()
+    try:
+        shutdown()          # no-op when the CLI already destroyed its process group
+    except Exception:
+        pass
     sys.exit(int(code or 0))

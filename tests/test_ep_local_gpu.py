@@ -223,32 +223,64 @@ def test_receive_bound_overflow_is_a_status_not_a_fault():
         buf.destroy()
 
 
-@pytest.mark.parametrize("chunks", [0, 1, 5, 32])
-def test_round_trip_for_several_combine_chunk_counts(chunks):
-    """The number of combine chunks only changes WHEN rows are returned and reduced, never what."""
+@pytest.mark.parametrize("R,T,H,E,K,dtype", [(1, 70, 256, 8, 2, torch.bfloat16), (4, 150, 1024, 32, 4, torch.bfloat16),
+                                             (8, 64, 7168, 64, 8, torch.bfloat16), (2, 100, 384, 8, 2, torch.float32)])
+def test_pull_combine_reads_rows_in_place_and_matches_the_oracle(R, T, H, E, K, dtype):
+    """Zero-copy dispatch output, modified in place by the 'expert', combined by the pull form
+    (no slot region): result and reduced side values equal the oracle. Three rounds with
+    different data, so a stale cached row from an earlier round would be seen."""
     from gpu_data_transfer_profile_b200.parallel.buffer import Buffer
-    R, T, H, E, K = 4, 150, 512, 32, 4
-    xs, idxs, ws = _mk(R, T, H, E, K, uneven=True, seed=5)
-    old = Buffer.combine_chunks
-    Buffer.combine_chunks = chunks
+    xs, idxs, ws = _mk(R, T, H, E, K, dtype, uneven=True, seed=7)
     g = _group(R)
     try:
-        cx, ci, cw = [x.cuda() for x in xs], [i.cuda() for i in idxs], [w.cuda() for w in ws]
-        ref = O.dispatch_rank_mode_ref(xs, idxs, ws, E)
+        ci, cw = [i.cuda() for i in idxs], [w.cuda() for w in ws]
         for rep in range(3):
+            cx = [(x.float() * (1 + rep)).to(dtype).cuda() for x in xs]
+            ref = O.dispatch_rank_mode_ref([c.cpu() for c in cx], idxs, ws, E)
             lays = g.get_dispatch_layout(ci, E)
-            outs = g.dispatch(cx, layouts=lays, topk_idx=ci, topk_weights=cw)
+            outs = g.dispatch(cx, layouts=lays, topk_idx=ci, topk_weights=cw, zero_copy=True)
             for d in range(R):
-                assert torch.equal(outs[d][0].cpu(), ref[d][0])
-            comb = g.combine([o[0] for o in outs], [o[4] for o in outs])
-            cref = O.combine_ref([r[0] for r in ref], [r[3] for r in ref], [r[4] for r in ref],
+                assert g.buffers[d]._use_pull(outs[d][0], outs[d][2])
+                outs[d][0].mul_(1 + d)                       # the "expert": in place, inside the region
+            ys = [o[0] for o in outs]
+            comb = g.combine(ys, [o[4] for o in outs], topk_weights=[o[2] for o in outs])
+            cref = O.combine_ref([(r[0].float() * (1 + d)).to(dtype) for d, r in enumerate(ref)],
+                                 [r[3] for r in ref], [r[4] for r in ref], [x.shape[0] for x in xs])
+            wref = O.combine_ref([r[2] for r in ref], [r[3] for r in ref], [r[4] for r in ref],
                                  [x.shape[0] for x in xs])
+            tol = 1e-5 if dtype == torch.float32 else 2e-2
             for s in range(R):
-                torch.testing.assert_close(comb[s][0].cpu().float(), cref[s], atol=0.16, rtol=2e-2)
+                got, got_w = comb[s]
+                torch.testing.assert_close(got.cpu().float(), cref[s], atol=tol * 16 * (1 + rep), rtol=tol)
+                torch.testing.assert_close(got_w.cpu(), wref[s], atol=1e-6, rtol=1e-6)
+        # forcing the push form on the same tensors gives the same numbers
+        old = Buffer.combine_transport
+        Buffer.combine_transport = "push"
+        try:
+            comb2 = g.combine(ys, [o[4] for o in outs], topk_weights=[o[2] for o in outs])
+        finally:
+            Buffer.combine_transport = old
+        for s in range(R):
+            assert torch.equal(comb2[s][0], comb[s][0])
         g.check_status()
     finally:
         g.destroy()
-        Buffer.combine_chunks = old
+
+
+def test_pull_combine_expert_mode_with_item_weights():
+    R, T, H, E, K = 4, 100, 512, 32, 4
+    xs, idxs, ws = _mk(R, T, H, E, K, zipf=1.2)
+    g = _group(R)
+    try:
+        cx, ci, cw = [x.cuda() for x in xs], [i.cuda() for i in idxs], [w.cuda() for w in ws]
+        outs = g.dispatch(cx, topk_idx=ci, topk_weights=cw, group_by_expert=True, num_experts=E, zero_copy=True)
+        assert all(g.buffers[d]._use_pull(outs[d][0], None) for d in range(R))
+        comb = g.combine([o[0] for o in outs], [o[4] for o in outs], item_weights=cw)
+        for s in range(R):
+            torch.testing.assert_close(comb[s][0].cpu().float(), xs[s].float(), atol=3e-2, rtol=2e-2)
+        g.check_status()
+    finally:
+        g.destroy()
 
 
 def test_dispatch_without_host_sync_num_worst_tokens():

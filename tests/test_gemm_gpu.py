@@ -134,6 +134,26 @@ def test_swiglu_fwd_bwd_kernels_match_autograd():
     torch.testing.assert_close(dp, rdp, atol=0.3, rtol=2e-2)
 
 
+@pytest.mark.parametrize("kind", ["gelu", "silu", "relu"])
+def test_ungated_activation_kernels_match_autograd(kind):
+    from gpu_data_transfer_profile_b200.models.experts import activate
+    from gpu_data_transfer_profile_b200.ops import gemm as G
+    torch.manual_seed(2)
+    rows, F = 77, 264
+    h = (torch.randn(rows, F, device="cuda") * 2).to(torch.bfloat16)
+    p = torch.rand(rows, device="cuda")
+    d = torch.randn(rows, F, device="cuda").to(torch.bfloat16)
+    act = G.act_fwd(h, p, kind)
+    hf = h.float().requires_grad_(True)
+    pf = p.clone().requires_grad_(True)
+    ref = activate(hf, kind) * pf[:, None]
+    torch.testing.assert_close(act.float(), ref.detach(), atol=2e-2, rtol=2e-2)
+    ref.backward(d.float())
+    dh, dp = G.act_bwd(h, p, d, kind)
+    torch.testing.assert_close(dh.float(), hf.grad, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(dp, pf.grad, atol=5e-2, rtol=2e-2)
+
+
 def test_tcgen05_experts_backward_matches_torch_experts():
     from gpu_data_transfer_profile_b200.models.experts import TorchGroupedExperts
     from gpu_data_transfer_profile_b200.models.experts_tcgen05 import Tcgen05GroupedExperts
@@ -162,14 +182,17 @@ def test_tcgen05_experts_backward_matches_torch_experts():
     torch.testing.assert_close(a.weight2.grad.float(), b.weight2.grad, atol=0.15, rtol=5e-2)
 
 
-def test_tcgen05_expert_mlp_gradients_match_fp32_autograd():
+@pytest.mark.parametrize("activation", ["swiglu", "gelu", "silu", "relu"])
+def test_tcgen05_expert_mlp_gradients_match_fp32_autograd(activation):
     """Training path of the expert MLP (tcgen05 forward, dgrads reading the weights in place,
-    ragged-reduction wgrads, fused SwiGLU backward) against fp32 autograd of the same math."""
+    ragged-reduction wgrads, fused activation backward) against fp32 autograd of the same math,
+    for every activation the reference's expert MLP offers."""
+    from gpu_data_transfer_profile_b200.models.experts import activate
     from gpu_data_transfer_profile_b200.models.experts_tcgen05 import Tcgen05GroupedExperts
     torch.manual_seed(5)
     H, F, counts = 256, 384, [70, 0, 301, 129]
     rows = sum(counts)
-    mod = Tcgen05GroupedExperts(len(counts), H, F, init_std=0.05)
+    mod = Tcgen05GroupedExperts(len(counts), H, F, init_std=0.05, activation=activation)
     x = torch.randn(rows, H, device="cuda").to(torch.bfloat16).requires_grad_(True)
     p = torch.rand(rows, device="cuda").requires_grad_(True)
     gy = torch.randn(rows, H, device="cuda").to(torch.bfloat16)
@@ -182,7 +205,7 @@ def test_tcgen05_expert_mlp_gradients_match_fp32_autograd():
     outs, r = [], 0
     for e, c in enumerate(counts):
         h = xf[r:r + c] @ w1[e].t()
-        a = torch.nn.functional.silu(h[:, :F]) * h[:, F:] * pf[r:r + c, None]
+        a = activate(h, activation) * pf[r:r + c, None]
         outs.append(a @ w2[e].t())
         r += c
     yr = torch.cat(outs)
@@ -192,3 +215,48 @@ def test_tcgen05_expert_mlp_gradients_match_fp32_autograd():
     torch.testing.assert_close(p.grad, pf.grad, atol=5e-2, rtol=5e-2)
     torch.testing.assert_close(mod.weight1.grad.float(), w1.grad, atol=6e-2, rtol=5e-2)
     torch.testing.assert_close(mod.weight2.grad.float(), w2.grad, atol=6e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("counts,N,K", [([128], 256, 128), ([200, 0, 57], 384, 512), ([1, 300, 129, 0], 256, 1024),
+                                        ([513], 128, 7168)])
+def test_grouped_gemm_fp8_block_scaled(counts, N, K, swiglu):
+    """e4m3 rows with 1x128 scales times e4m3 weights with 128x128 scales, against the fp32 matmul
+    of the DEQUANTISED operands (the kernel multiplies exactly those numbers, so only the
+    accumulation order and the bf16 store differ). Ragged counts with an empty expert."""
+    from gpu_data_transfer_profile_b200.ops import gemm as G
+    torch.manual_seed(11)
+    rows, E = sum(counts), len(counts)
+    Nw = 2 * N if swiglu else N
+    x = torch.randn(rows + 5, K, device="cuda") * (1 + torch.arange(K, device="cuda") % 7)     # uneven block scales
+    w = torch.randn(E, Nw, K, device="cuda") * 0.05
+    xq, xs = G.quantize_rows_1x128(x)
+    wq, ws = G.quantize_weights_128x128(w)
+    p = torch.rand(rows + 5, device="cuda")
+    off = G.offsets_from_counts(counts, "cuda")
+    out = torch.full((rows + 5, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    G.grouped_gemm_fp8(xq, xs, wq, ws, off, swiglu=swiglu, row_prob=p if swiglu else None, out=out)
+    xd = (xq.float().view(rows + 5, K // 128, 128) * xs[..., None]).view(rows + 5, K)
+    wd = G.dequantize_weights_128x128(wq, ws)
+    r = 0
+    for e, c in enumerate(counts):
+        h = xd[r:r + c] @ wd[e].t()
+        ref = torch.nn.functional.silu(h[:, :N]) * h[:, N:] * p[r:r + c, None] if swiglu else h
+        torch.testing.assert_close(out[r:r + c].float(), ref, atol=2e-2 * float(ref.abs().max() + 1), rtol=2e-2)
+        r += c
+    assert bool((out[rows:] == 7.0).all())           # rows beyond the last expert are never written
+
+
+def test_tcgen05_experts_consume_fp8_dispatch_rows():
+    from gpu_data_transfer_profile_b200.models.experts_tcgen05 import Tcgen05GroupedExperts
+    from gpu_data_transfer_profile_b200.ops import gemm as G
+    torch.manual_seed(3)
+    H, F, counts = 512, 256, [90, 0, 200, 33]
+    rows = sum(counts)
+    mod = Tcgen05GroupedExperts(len(counts), H, F, init_std=0.05, use_fp8=True)
+    x = torch.randn(rows, H, device="cuda").to(torch.bfloat16)
+    p = torch.rand(rows, device="cuda")
+    xq, xs = G.quantize_rows_1x128(x)
+    y = mod((xq, xs), counts, p)
+    y_ref = mod(x, counts, p)                              # bf16 path on the unquantised rows
+    torch.testing.assert_close(y.float(), y_ref.float(), atol=0.08 * float(y_ref.float().abs().max()), rtol=0.1)

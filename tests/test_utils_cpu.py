@@ -208,6 +208,6 @@ def test_control_area_blocks_have_shape_independent_positions():
     from gpu_data_transfer_profile_b200.parallel.buffer import _Carve
     a = _Carve(64 << 20, 8, 256, 8, 1024, 2048, 2048)
     b = _Carve(64 << 20, 2, 8, 2, 512, 1024, 1024)
-    assert (a.flags, a.chunk_flags, a.recv_bnd) == (b.flags, b.chunk_flags, b.recv_bnd)
-    assert a.recv_bnd[1] < a.counts[0] and a.counts[1] < a.ll_ctrl
+    assert (a.flags, a.pull_info) == (b.flags, b.pull_info)
+    assert a.pull_info < a.counts[0] and a.counts[1] < a.ll_ctrl
     assert _Carve(64 << 20, 8, 256, 8, 1024, 2048, 2048, max_recv_rows=100).cap == 100
