@@ -71,7 +71,7 @@ __device__ __forceinline__ bool decode_tile(int t, const int* s_tile_off, const 
   return true;
 }
 
-__device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
+__device__ __forceinline__ float silu(float v) { return __fdividef(v, 1.f + __expf(-v)); }
 
 // e4m3 x e4m3 -> f32, K-major operands, tile M x N
 __device__ __forceinline__ uint32_t instr_desc_e4m3(int M, int N) {
@@ -204,6 +204,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       const float* sw_a = p.sw + ((size_t)tl.e * (p.w_rows / 128) + wblk_a) * k_blocks;
       const float* sw_b = p.sw + ((size_t)tl.e * (p.w_rows / 128) + wblk_b) * k_blocks;
       const float* sa_row = p.sa + (size_t)my_row * kb_ld;
+      // the row's routing probability is needed only after the last block: fetch it now
+      float prob = 1.f;
+      if (EPI == EPI_SWIGLU && row_ok && p.row_prob) prob = __ldg(p.row_prob + my_row);
       float acc[128];
 #pragma unroll
       for (int i = 0; i < 128; ++i) acc[i] = 0.f;
@@ -217,24 +220,38 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         if (!mbar_wait(&part_full[buf], (it >> 1) & 1, p.status, abort)) { ok = false; break; }
         fence_after_sync();
         const uint32_t t_addr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
+        // four loads of 32 columns, software-pipelined: the next load is in flight while the
+        // previous one is folded into the running sums
+        const uint32_t c0 = t_addr + col_a, c1 = t_addr + col_a + 32, c2 = t_addr + col_b, c3 = t_addr + col_b + 32;
+        uint32_t v0[32], v1[32];
+        tmem_ld32(c0, v0);
+        tmem_ld_wait();
+        tmem_ld_pin(v0);
+        tmem_ld32(c1, v1);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld32(t_addr + (c < 2 ? col_a + c * 32 : col_b + (c - 2) * 32), v);
-          tmem_ld_wait();
-          const float f = c < 2 ? fa : fb;
+        for (int i = 0; i < 32; ++i) acc[i] = fmaf(fa, __uint_as_float(v0[i]), acc[i]);
+        tmem_ld_wait();
+        tmem_ld_pin(v1);
+        tmem_ld32(c2, v0);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(f, __uint_as_float(v[i]), acc[c * 32 + i]);
-        }
+        for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(fa, __uint_as_float(v1[i]), acc[32 + i]);
+        tmem_ld_wait();
+        tmem_ld_pin(v0);
+        tmem_ld32(c3, v1);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(fb, __uint_as_float(v0[i]), acc[64 + i]);
+        tmem_ld_wait();
+        tmem_ld_pin(v1);
+        // every TMEM read of this block is done: hand the buffer back BEFORE the last fold
         fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&part_empty[buf]);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(fb, __uint_as_float(v1[i]), acc[96 + i]);
       }
       if (!ok) break;
       if (tl.valid_rows <= 0) continue;
       // ---- store: EPI_COLS output columns per pass through the per-warp staging tile ----
-      float prob = 1.f;
-      if (EPI == EPI_SWIGLU && row_ok && p.row_prob) prob = p.row_prob[my_row];
       constexpr int PASSES = ((EPI == EPI_SWIGLU) ? 64 : 128) / EPI_COLS;
 #pragma unroll
       for (int ps = 0; ps < PASSES; ++ps) {

@@ -53,6 +53,8 @@ def main() -> int:
     ap.add_argument("--wgrad", action="store_true", help="also time the two weight-gradient GEMMs (ragged reduction)")
     ap.add_argument("--form", choices=["cta", "pair", "both"], default="both",
                     help="cta: one CTA per 128x256 tile; pair: a CTA pair (cta_group::2) per 256x256 tile")
+    ap.add_argument("--fp8", action="store_true",
+                    help="also time the block-scaled fp8 fc1 (e4m3 rows with 1x128 scales, e4m3 weights with 128x128 scales)")
     ap.add_argument("--band-mb", type=str, default="",
                     help="comma-separated L2 band sizes (MiB) of the tile order to compare; empty = the default")
     args = ap.parse_args()
@@ -72,7 +74,7 @@ def main() -> int:
     p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
     if os.path.exists(p):
         peaks = json.load(open(p))
-    peak = peaks.get("bf16_tflops", 1590.0)
+    peak = peaks.get("bf16_tflops", 1590.0)      # fp8 rows are reported against the same (bf16) figure
     f1 = 2.0 * rows * H * 2 * F
     f2 = 2.0 * rows * F * H
     bands = [int(float(b) * (1 << 20)) for b in args.band_mb.split(",") if b] or [None]
@@ -86,6 +88,14 @@ def main() -> int:
             fns["fc2_tcgen05" + tag] = (
                 lambda pair=pair, band=band: G.grouped_gemm(act, w2, off, out=out, pair=pair, band_bytes=band))
             flops["fc1_swiglu_tcgen05" + tag], flops["fc2_tcgen05" + tag] = f1, f2
+    if args.fp8:
+        xq, xs = G.quantize_rows_1x128(x)
+        wq, ws = G.quantize_weights_128x128(w1)
+        fns["fc1_swiglu_fp8_tcgen05"] = lambda: G.grouped_gemm_fp8(xq, xs, wq, ws, off, swiglu=True, row_prob=prob, out=act)
+        flops["fc1_swiglu_fp8_tcgen05"] = f1
+        hpl = torch.empty(rows, 2 * F, dtype=torch.bfloat16, device=dev)
+        fns["fc1_plain_fp8_tcgen05"] = lambda: G.grouped_gemm_fp8(xq, xs, wq, ws, off, out=hpl)
+        flops["fc1_plain_fp8_tcgen05"] = f1
     if args.wgrad:
         dh = torch.randn(rows, 2 * F, device=dev).to(torch.bfloat16)
         dy = torch.randn(rows, H, device=dev).to(torch.bfloat16)

@@ -240,6 +240,8 @@ def test_grouped_gemm_fp8_block_scaled(counts, N, K, swiglu):
     wd = G.dequantize_weights_128x128(wq, ws)
     r = 0
     for e, c in enumerate(counts):
+        if c == 0:
+            continue
         h = xd[r:r + c] @ wd[e].t()
         ref = torch.nn.functional.silu(h[:, :N]) * h[:, N:] * p[r:r + c, None] if swiglu else h
         torch.testing.assert_close(out[r:r + c].float(), ref, atol=2e-2 * float(ref.abs().max() + 1), rtol=2e-2)
