@@ -78,12 +78,14 @@ def main() -> int:
     T, H, E, K = args.tokens, args.hidden, args.experts, args.topk
     Buffer.set_num_sms(args.num_sms if args.num_sms > 0 else 132)
 
-    cfg = Buffer.get_dispatch_config(world, T, K, E)
+    # The step combines the zero-copy receive rows in place (pull form), so the buffer needs no
+    # combine slots: that halves the symmetric region (worst-case receive rows x 2 epoch parities).
+    cfg = Buffer.get_dispatch_config(world, T, K, E, combine_slots=False)
     nbytes = cfg.get_nvl_buffer_size_hint(H * 2, world)
     if world > 1:
-        buf = Buffer(torch.distributed.group.WORLD, nbytes, 0)
+        buf = Buffer(torch.distributed.group.WORLD, nbytes, 0, combine_slots=False)
     else:
-        buf = Buffer(None, nbytes, 0, world=LocalWorld.make(1, dev)[0])
+        buf = Buffer(None, nbytes, 0, world=LocalWorld.make(1, dev)[0], combine_slots=False)
 
     # ---- seeded synthetic inputs, staged in pinned host memory for the end-to-end arm ----
     g = torch.Generator().manual_seed(1234 + rank)

@@ -65,8 +65,15 @@ CeEngine::CeEngine(std::vector<CeCopy> copies, int mode, int stream_device, bool
       h[i].src = reinterpret_cast<const void*>(copies_[i].src);
       h[i].nbytes = (long long)copies_[i].nbytes;
     }
-    cudaMalloc(&desc_dev_, h.size() * sizeof(CopyDesc));
-    cudaMemcpy(desc_dev_, h.data(), h.size() * sizeof(CopyDesc), cudaMemcpyHostToDevice);
+    cudaError_t e = cudaMalloc(&desc_dev_, h.size() * sizeof(CopyDesc));
+    if (e == cudaSuccess) e = cudaMemcpy(desc_dev_, h.data(), h.size() * sizeof(CopyDesc), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+      // without a valid table the kernel must never be launched: enqueue_once() refuses on a null table
+      cudaGetLastError();
+      if (desc_dev_) cudaFree(desc_dev_);
+      desc_dev_ = nullptr;
+      last_where_ = std::string("descriptor table: ") + cudaGetErrorString(e);
+    }
   }
   cudaSetDevice(prev);
   if (use_proxy_) proxy_ = std::thread(&CeEngine::proxy_main, this);
@@ -99,6 +106,10 @@ int CeEngine::enqueue_once() {
     cudaError_t e = cudaGraphLaunch(graph_exec_, stream_);
     if (e != cudaSuccess) last_where_ = "cudaGraphLaunch";
     return (int)e;
+  }
+  if (desc_dev_ == nullptr) {
+    if (last_where_.empty()) last_where_ = "descriptor table not allocated";
+    return (int)cudaErrorInvalidValue;
   }
   if (launch_batched_copy(static_cast<const CopyDesc*>(desc_dev_), (int)copies_.size(), ctas_,
                           threads_, stream_) != 0) {

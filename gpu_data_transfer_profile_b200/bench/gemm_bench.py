@@ -53,6 +53,7 @@ def main() -> int:
     ap.add_argument("--wgrad", action="store_true", help="also time the two weight-gradient GEMMs (ragged reduction)")
     ap.add_argument("--form", choices=["cta", "pair", "both"], default="both",
                     help="cta: one CTA per 128x256 tile; pair: a CTA pair (cta_group::2) per 256x256 tile")
+    ap.add_argument("--peaks", default=None, help="JSON file with {bf16_tflops: measured library GEMM rate}")
     ap.add_argument("--fp8", action="store_true",
                     help="also time the block-scaled fp8 fc1 (e4m3 rows with 1x128 scales, e4m3 weights with 128x128 scales)")
     ap.add_argument("--band-mb", type=str, default="",
@@ -71,10 +72,11 @@ def main() -> int:
     out = torch.empty(rows, H, dtype=torch.bfloat16, device=dev)
     flush = L2Flusher(dev)
     peaks = {}
-    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
-    if os.path.exists(p):
-        peaks = json.load(open(p))
-    peak = peaks.get("bf16_tflops", 1590.0)      # fp8 rows are reported against the same (bf16) figure
+    if args.peaks and os.path.exists(args.peaks):
+        peaks = json.load(open(args.peaks))
+    # fraction denominator: the measured library bf16 GEMM rate of this machine when a peaks file is
+    # given, else 1590 TFLOP/s (an earlier measurement on the same kind of GPU); fp8 rows use it too
+    peak = peaks.get("bf16_tflops", 1590.0)
     f1 = 2.0 * rows * H * 2 * F
     f2 = 2.0 * rows * F * H
     bands = [int(float(b) * (1 << 20)) for b in args.band_mb.split(",") if b] or [None]

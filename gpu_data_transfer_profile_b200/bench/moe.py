@@ -37,9 +37,18 @@ class IterationResult:
 def run_one_iteration(ctx, manager, experts, args, x, fused: bool) -> IterationResult:
     e0, e1, e2, e3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
     e0.record()
-    rows, tpe, probs = manager.dispatch(x, ctx.topk_idx, ctx.topk_weights)
+    fp8 = getattr(args, "fp8", False) and not args.backward
+    if fp8:
+        rows, tpe, probs = manager.dispatch_fp8(x, ctx.topk_idx, ctx.topk_weights)
+    else:
+        rows, tpe, probs = manager.dispatch(x, ctx.topk_idx, ctx.topk_weights)
     e1.record()
-    if fused:
+    if fp8:
+        El = experts.num_local_experts
+        y = experts.forward_fp8(rows, tpe, probs, expert_off=manager.handle.meta[2 + El: 2 + El + El + 1])
+        e2.record()
+        out = manager.combine(y)
+    elif fused:
         buf = A.get_buffer(manager.group, A.get_hidden_bytes(x), manager.world)
         handle, manager.handle = manager.handle, None
         if args.backward:
@@ -71,6 +80,8 @@ def main() -> int:
     ap.add_argument("--dispatcher-mode", choices=("fused", "deepep"), default="fused")
     ap.add_argument("--fuse-combine", action="store_true")
     ap.add_argument("--backward", action="store_true")
+    ap.add_argument("--fp8", action="store_true",
+                    help="forward only: e4m3 dispatch (1x128 scales) feeding the block-scaled fp8 fc1 on the tensor cores")
     args = ap.parse_args()
     rank, world, _ = D.init_distributed()
     C.validate_args(args, world)
@@ -86,7 +97,9 @@ def main() -> int:
     manager = B200TokenDispatcher(group, El, E, ep_rank * El, args.async_finish, args.allocate_on_comm_stream,
                                   mode=args.dispatcher_mode, world=lworld)
     dtype = C.DTYPES[args.dtype]
-    experts, backend = build_experts(args.expert_backend, El, H, F, dtype, args.activation, dev)
+    experts, backend = build_experts(args.expert_backend, El, H, F, dtype, args.activation, dev, use_fp8=args.fp8)
+    if args.fp8 and not getattr(experts, "use_fp8", False):
+        raise ValueError("--fp8 needs the tcgen05 expert backend (hidden and ffn sizes multiples of 128)")
 
     class Ctx:
         pass
@@ -126,7 +139,7 @@ def main() -> int:
     all_ok = D.all_ranks_boolean(ok)
     flops = 2.0 * int(last.tokens_per_expert.sum()) * H * F * (3 if args.activation == "swiglu" else 2)
     C.emit(rank, dict(bench="moe", ep=args.ep, tokens=T, hidden=H, ffn=F, experts=E, topk=K, backend=backend,
-                      mode=args.dispatcher_mode, fused_combine=fused, backward=args.backward,
+                      mode=args.dispatcher_mode, fused_combine=fused, backward=args.backward, fp8=args.fp8,
                       dispatch_ms=acc[0], expert_ms=acc[1], combine_ms=acc[2], total_ms_rank0=acc[3],
                       total_ms_max_over_ranks=tot_max,
                       fwd_bwd_ms_max_over_ranks=D.all_reduce_scalar(acc[4], "max", group) if args.backward else None, expert_tflops_rank0=flops / (acc[1] * 1e-3) / 1e12 if acc[1] else 0,

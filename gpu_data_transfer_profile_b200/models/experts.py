@@ -73,13 +73,14 @@ class TorchGroupedExperts(GroupedExpertsBase):
 
 
 def build_experts(backend: str, num_local_experts: int, hidden_size: int, ffn_hidden_size: int,
-                  dtype: torch.dtype, activation: str, device="cuda") -> Tuple[torch.nn.Module, str]:
+                  dtype: torch.dtype, activation: str, device="cuda", use_fp8: bool = False) -> Tuple[torch.nn.Module, str]:
     """backend: 'auto' | 'tcgen05' | 'torch' ('te' is accepted as an alias of 'auto': the library
     grouped GEMM of the reference is replaced by this repository's own kernels)."""
     if backend in ("auto", "tcgen05", "te"):
         try:
             from .experts_tcgen05 import Tcgen05GroupedExperts
-            return (Tcgen05GroupedExperts(num_local_experts, hidden_size, ffn_hidden_size, dtype, activation, device),
+            return (Tcgen05GroupedExperts(num_local_experts, hidden_size, ffn_hidden_size, dtype, activation, device,
+                                          use_fp8=use_fp8),
                     "tcgen05_grouped_gemm")
         except Exception as exc:  # unsupported shape/dtype or extension not built
             if backend == "tcgen05":

@@ -104,6 +104,21 @@ class B200TokenDispatcher:
         self.handle, self.tokens_per_expert, self.dispatched_probs = handle, tpe, row_probs
         return rows, tpe, row_probs
 
+    @torch.no_grad()
+    def dispatch_fp8(self, hidden_states, token_indices, token_probs):
+        """Forward-only, fused mode: the dispatch kernel casts every row to e4m3 with one f32 scale
+        per 128 channels on its way out. Returns ((rows e4m3 [N,H], scales f32 [N,H/128]),
+        tokens_per_expert, one probability per row); `combine` then takes the experts' bf16 output."""
+        if self.mode != "fused":
+            raise ValueError("fp8 dispatch is offered by the fused (expert-grouped) dispatcher")
+        buf = A.get_buffer(self.group, A.get_hidden_bytes(hidden_states), self.world)
+        rows, _, _, per_local, handle, _ = buf.dispatch(
+            hidden_states.contiguous(), topk_idx=token_indices.contiguous(), topk_weights=token_probs.contiguous().float(),
+            group_by_expert=True, num_experts=self.num_experts, use_fp8=True)
+        tpe = torch.tensor(per_local, dtype=torch.int64)
+        self.handle, self.tokens_per_expert, self.dispatched_probs = handle, tpe, handle.recv_prob
+        return rows, tpe, handle.recv_prob
+
     def combine(self, hidden_states):
         if self.handle is None:
             raise RuntimeError("combine() called before dispatch()")

@@ -87,7 +87,7 @@ class _Carve:
     flags and the pull-combine announcements. The count matrices follow."""
 
     def __init__(self, nbytes: int, R: int, E: int, K: int, H: int, row_bytes: int, comb_row_bytes: int,
-                 max_recv_rows: int = 0):
+                 max_recv_rows: int = 0, combine_slots: bool = True):
         C = _ext.load()
         self.key = (E, K, H, row_bytes, comb_row_bytes)
         self.flags = 0
@@ -102,13 +102,16 @@ class _Carve:
             raise ValueError("too many experts/ranks for the fixed control area")
         self.scale_cols = max(H // 128, 1)
         sizes = dict(recv_x=row_bytes, recv_scales=self.scale_cols * 4, recv_topk_idx=K * 8,
-                     recv_topk_w=K * 4, recv_meta=8, recv_prob=4, comb_x=comb_row_bytes, comb_w=K * 4)
+                     recv_topk_w=K * 4, recv_meta=8, recv_prob=4,
+                     comb_x=comb_row_bytes if combine_slots else 0, comb_w=K * 4 if combine_slots else 0)
+        self.combine_slots = bool(combine_slots)
         per_row = sum(sizes.values())
         avail = nbytes - FIXED_BYTES - 2 * len(sizes) * REGION_ALIGN
         self.cap = max(avail // (2 * per_row), 0)
         if max_recv_rows > 0:
             self.cap = min(self.cap, int(max_recv_rows))
-        self.slot_cap = self.cap
+        # without slots the slot numbers that dispatch computes are never used as addresses
+        self.slot_cap = self.cap if combine_slots else (1 << 30)
         self.regions = []  # per parity: dict name -> offset
         off = FIXED_BYTES
         for _ in range(2):
@@ -173,22 +176,24 @@ class Buffer:
     @staticmethod
     def get_dispatch_config(group_size: int, num_max_tokens_per_rank: int = 4096, num_topk: int = 8,
                             num_experts: int = 256, group_by_expert: bool = False,
-                            num_max_recv_tokens: int = 0) -> Config:
+                            num_max_recv_tokens: int = 0, combine_slots: bool = True) -> Config:
         return Config(Buffer.num_sms, num_max_tokens_per_rank, num_topk, num_experts,
-                      group_by_expert=group_by_expert, num_max_recv_tokens=num_max_recv_tokens)
+                      group_by_expert=group_by_expert, num_max_recv_tokens=num_max_recv_tokens,
+                      combine_slots=combine_slots)
 
     @staticmethod
     def get_combine_config(group_size: int, num_max_tokens_per_rank: int = 4096, num_topk: int = 8,
                            num_experts: int = 256, group_by_expert: bool = False,
-                           num_max_recv_tokens: int = 0) -> Config:
+                           num_max_recv_tokens: int = 0, combine_slots: bool = True) -> Config:
         return Config(Buffer.num_sms, num_max_tokens_per_rank, num_topk, num_experts,
-                      group_by_expert=group_by_expert, num_max_recv_tokens=num_max_recv_tokens)
+                      group_by_expert=group_by_expert, num_max_recv_tokens=num_max_recv_tokens,
+                      combine_slots=combine_slots)
 
     # ---- construction ----------------------------------------------------------------
     def __init__(self, group=None, num_nvl_bytes: int = 0, num_rdma_bytes: int = 0,
                  low_latency_mode: bool = False, num_qps_per_rank: int = 1, *,
                  world=None, timeout_s: float = 20.0, blocks_per_sm: int = 2,
-                 num_max_recv_tokens: int = 0):
+                 num_max_recv_tokens: int = 0, combine_slots: bool = True):
         self.C = _ext.load()
         self.world = world if world is not None else ProcessWorld(group)
         self.group = group
@@ -202,6 +207,7 @@ class Buffer:
         self.timeout_s = float(timeout_s)
         self.blocks_per_sm = blocks_per_sm
         self.num_max_recv_tokens = int(num_max_recv_tokens)
+        self.combine_slots = bool(combine_slots)
         if self.num_nvl_bytes < FIXED_BYTES + REGION_ALIGN:
             raise ValueError("num_nvl_bytes too small; use Config.get_nvl_buffer_size_hint")
         self.region = SymmetricRegion(self.world, self.num_nvl_bytes)
@@ -288,7 +294,7 @@ class Buffer:
                 self.barrier()           # region reuse with another shape: drain every rank first
             self._ll = None
             self._carve = _Carve(self.num_nvl_bytes, self.group_size, E, K, H, row_bytes, comb_row_bytes,
-                                 self.num_max_recv_tokens)
+                                 self.num_max_recv_tokens, self.combine_slots)
         return self._carve
 
     def _geom(self, *, E, K, T, mode, H, cap, slot_cap, epoch, epoch_wait=0, tail_wait=0) -> List[int]:
@@ -605,6 +611,8 @@ class Buffer:
         carve = self._carve
         if carve is None or carve.key[:3] != (handle.E, handle.K, handle.H):
             raise ValueError("combine must follow a dispatch of the same shape on this buffer")
+        if not carve.combine_slots:
+            raise ValueError("this buffer has no combine slots: only the pull form of combine is available")
         if handle.H * x.element_size() > carve.key[4]:
             raise ValueError("combine dtype is wider than the region reserved at dispatch")
         self._epoch["combine"] += 1
@@ -664,8 +672,9 @@ class Buffer:
             return False
         ok = self._region_offset(x) >= 0 and x.data_ptr() % 16 == 0 and (
             topk_weights is None or (topk_weights.dtype == torch.float32 and self._region_offset(topk_weights) >= 0))
-        if mode == "pull" and not ok:
-            raise ValueError("combine_transport='pull' needs x (and topk_weights) inside the symmetric region")
+        if (mode == "pull" or not self.combine_slots) and not ok:
+            raise ValueError("this combine can only pull (combine_transport='pull' or a buffer without combine "
+                             "slots): x (and topk_weights) must lie inside the symmetric region")
         return ok
 
     def _combine_pull(self, phase: int, x, handle: DispatchHandle, topk_weights, weights=None, out=None):
@@ -697,8 +706,8 @@ class Buffer:
         slot area of the next combine's parity: valid until that combine returns, and only for
         callers that then combine this very tensor."""
         carve = self._carve
-        if carve is None:
-            raise ValueError("combine_input() must follow a dispatch on this buffer")
+        if carve is None or not carve.combine_slots:
+            raise ValueError("combine_input() must follow a dispatch on a buffer that has combine slots")
         es = torch.empty((), dtype=dtype).element_size()
         if num_rows * hidden * es > carve.slot_cap * carve.key[4]:
             raise ValueError("combine_input larger than the combine area of this buffer")
@@ -972,39 +981,47 @@ class _LLCarve:
         self.comb_in = off          # [El][R*M][H] bf16: where the experts write when combine pulls
 
 
-def _fused_fc2_combine(self: Buffer, act: torch.Tensor, w2: torch.Tensor, handle: DispatchHandle,
-                       item_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+def _fused_fc2_send(self: Buffer, act: torch.Tensor, w2: torch.Tensor, handle: DispatchHandle):
     """fc2 grouped GEMM whose epilogue IS the combine send: each output tile row is stored
     straight into its token's slot on the source rank (peer LSU stores from the tensor-core
-    kernel), the last CTA raises the combine flags, and the source reduces on arrival.
-    act: bf16 [N_recv, F] rows grouped by local expert (expert-mode handle), w2: bf16 [E_local, H, F].
-    Returns combined [T, H] bf16."""
+    kernel) and the last CTA raises this rank's combine flag on every peer. Returns the state that
+    `_combine_p2` (the reduce half) needs."""
     from ..ops import gemm as G
     if handle.mode != 1:
         raise ValueError("fused fc2+combine needs an expert-grouped dispatch handle")
     carve = self._carve
     if carve is None or carve.key[:3] != (handle.E, handle.K, handle.H):
         raise ValueError("fused combine must follow a dispatch of the same shape on this buffer")
+    if not carve.combine_slots:
+        raise ValueError("the fc2 epilogue stores into combine slots, which this buffer does not have")
     if w2.shape[1] != handle.H or act.dtype != torch.bfloat16:
         raise ValueError("w2 must be [E_local, hidden, ffn] and act bf16")
+    self._epoch["combine"] += 1
+    ep = self._epoch["combine"]
+    regions = carve.region_list(0, 0, ep & 1)
+    El = handle.E // self.group_size
+    expert_off = handle.meta[2 + El: 2 + El + El + 1]
+    flag_row = self.C.MAX_RANKS * 4 * 2          # byte offset of the combine channel's flag row
+    G.grouped_gemm_combine(act, w2, expert_off, handle.recv_meta, self.peers, regions[8], carve.slot_cap,
+                           self.rank, signal_flag_off=flag_row, epoch=ep, counter=self.counters[3:4],
+                           status_ptr=self.status_ptr)
+    geom = self._geom(E=handle.E, K=handle.K, T=handle.T, mode=1, H=handle.H, cap=handle.n_recv,
+                      slot_cap=carve.slot_cap, epoch=ep)
+    return dict(ep=ep, regions=regions, geom=geom, dtype=torch.bfloat16, topk_w=None)
+
+
+def _fused_fc2_combine(self: Buffer, act: torch.Tensor, w2: torch.Tensor, handle: DispatchHandle,
+                       item_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fc2 with the combine send in its epilogue, then the reduction on arrival of this rank's own
+    tokens. act: bf16 [N_recv, F] rows grouped by local expert (expert-mode handle), w2: bf16
+    [E_local, H, F]. Returns combined [T, H] bf16."""
     compute = self._enter(None, False, False)
     with torch.cuda.stream(self.comm_stream):
-        self._epoch["combine"] += 1
-        ep = self._epoch["combine"]
-        regions = carve.region_list(0, 0, ep & 1)
-        El = handle.E // self.group_size
-        expert_off = handle.meta[2 + El: 2 + El + El + 1]
-        flag_row = self.C.MAX_RANKS * 4 * 2          # byte offset of the combine channel's flag row
-        G.grouped_gemm_combine(act, w2, expert_off, handle.recv_meta, self.peers, regions[8], carve.slot_cap,
-                               self.rank, signal_flag_off=flag_row, epoch=ep, counter=self.counters[3:4],
-                               status_ptr=self.status_ptr)
-        geom = self._geom(E=handle.E, K=handle.K, T=handle.T, mode=1, H=handle.H, cap=handle.n_recv,
-                          slot_cap=carve.slot_cap, epoch=ep)
-        # the GEMM's last CTA raises one flag per rank: the reduce launch waits for those
-        st = dict(ep=ep, regions=regions, geom=geom, dtype=torch.bfloat16, topk_w=None)
+        st = _fused_fc2_send(self, act, w2, handle)
         out, _ = self._combine_p2(st, handle, item_weights)
     self._exit(compute, False, [out, act])
     return out
 
 
+Buffer._fused_fc2_send = _fused_fc2_send
 Buffer.fused_fc2_combine = _fused_fc2_combine

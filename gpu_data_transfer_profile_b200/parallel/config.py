@@ -29,6 +29,10 @@ class Config:
     # every rank lands here). A routing that exceeds the bound ends in status 6 (receive overflow),
     # never in an out-of-range store. Pass the same value to `Buffer(num_max_recv_tokens=...)`.
     num_max_recv_tokens: int = 0
+    # False: reserve no combine slots. Combine is then only possible in its pull form (rows read in
+    # place from the producers' receive regions), which needs no slots; the region is about half
+    # the size. Pass the same value to `Buffer(combine_slots=...)`.
+    combine_slots: bool = True
 
     def per_row_bytes(self, hidden_bytes: int) -> int:
         """Bytes that one receive row plus one combine slot occupy (all side arrays)."""
@@ -36,7 +40,7 @@ class Config:
         hidden_elems = max(hidden_bytes // 2, 1)
         scales = ((hidden_elems + 127) // 128) * 4
         recv = hidden_bytes + scales + k * 8 + k * 4 + 8 + 4
-        comb = hidden_elems * max(self.combine_elem_bytes, 2) + k * 4
+        comb = (hidden_elems * max(self.combine_elem_bytes, 2) + k * 4) if self.combine_slots else 0
         return align_up(recv, 16) + align_up(comb, 16) + 64
 
     def get_nvl_buffer_size_hint(self, hidden_bytes: int, group_size: int) -> int:

@@ -54,6 +54,13 @@ class LocalGroup:
         return [b._combine_p2(sts[r], handles[r], item_weights[r] if item_weights is not None else None)
                 for r, b in enumerate(self.buffers)]
 
+    def fused_fc2_combine(self, acts, w2s, handles, item_weights=None):
+        """fc2 GEMMs whose epilogues store into the other virtual ranks' slots (all ranks first),
+        then every rank's reduction."""
+        sts = [b._fused_fc2_send(acts[r], w2s[r], handles[r]) for r, b in enumerate(self.buffers)]
+        return [b._combine_p2(sts[r], handles[r], item_weights[r] if item_weights is not None else None)[0]
+                for r, b in enumerate(self.buffers)]
+
     def low_latency_dispatch(self, xs, topk_idx, num_max_tokens: int, num_experts: int, use_fp8=True):
         for r, b in enumerate(self.buffers):     # every virtual rank prepares its regions before anyone sends
             b._ll_state(num_experts, topk_idx[r].shape[1], xs[r].shape[1], num_max_tokens)

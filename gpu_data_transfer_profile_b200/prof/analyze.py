@@ -25,7 +25,8 @@ from typing import Any, Dict, List, Optional
 from . import nsys_sqlite as N
 
 KERNEL_CANDIDATES = ("lsu_rr_copy_kernel", "tma_staged_push_kernel", "tma_staged_pull_kernel", "lsu_copy_kernel",
-                     "batched_copy_kernel", "dispatch_send_kernel", "combine_send_kernel", "grouped_gemm_kernel",
+                     "batched_copy_kernel", "dispatch_send_kernel", "combine_kernel", "combine_pull_kernel", "grouped_gemm_kernel",
+                     "grouped_gemm_fp8_kernel",
                      "lsu_round_robin_copy_kernel", "tma_round_robin_copy_kernel", "tma_copy_kernel")
 
 

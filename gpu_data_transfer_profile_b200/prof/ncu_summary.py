@@ -70,9 +70,10 @@ def main(argv=None) -> int:
     ap.add_argument("--kernel", default="")
     ap.add_argument("--flops", type=float, default=0.0, help="algorithmic FLOPs per launch")
     ap.add_argument("--bytes", type=float, default=0.0, help="algorithmic bytes per launch")
-    ap.add_argument("--peaks", default="MEASURED_PEAKS.json")
+    ap.add_argument("--peaks", default=None,
+                    help="JSON file with measured peaks {hbm_gbs, bf16_tflops}; without it no fraction is printed")
     a = ap.parse_args(argv)
-    peaks = json.load(open(a.peaks)) if os.path.exists(a.peaks) else {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    peaks = json.load(open(a.peaks)) if a.peaks and os.path.exists(a.peaks) else None
     for d in summarize(read_raw(a.raw_csv), a.kernel, a.flops, a.bytes, peaks):
         print(json.dumps(d))
     return 0

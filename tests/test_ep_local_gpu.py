@@ -359,3 +359,64 @@ def test_round_trip_is_independent_of_the_cta_knob(num_sms):
     finally:
         g.destroy()
         Buffer.set_num_sms(old)
+
+
+@pytest.mark.parametrize("R", [2, 4])
+def test_fc2_epilogue_combine_addresses_every_virtual_rank(R):
+    """The fc2 grouped GEMM's combine epilogue stores each output row into its token's slot on the
+    SOURCE rank; with several virtual ranks the slots live in different regions, so the peer
+    addressing of the epilogue is exercised on one GPU. Oracle: per-expert fp32 matmul of the
+    dispatched rows, summed per token by the list-based combine oracle."""
+    T, H, F, E, K = 120, 256, 256, 8, 2
+    xs, idxs, ws = _mk(R, T, H, E, K, seed=9)
+    El = E // R
+    g = _group(R)
+    try:
+        cx, ci, cw = [x.cuda() for x in xs], [i.cuda() for i in idxs], [w.cuda() for w in ws]
+        outs = g.dispatch(cx, topk_idx=ci, topk_weights=cw, group_by_expert=True, num_experts=E)
+        ref = O.dispatch_expert_mode_ref(xs, idxs, ws, E)
+        torch.manual_seed(1)
+        w2s = [(torch.randn(El, H, H, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(R)]
+        acts = [o[0] for o in outs]                     # stand-in for the fc1 output: F == H here
+        comb = g.fused_fc2_combine(acts, w2s, [o[4] for o in outs])
+        ys = []
+        for d in range(R):
+            ex, ep, sr, stok, sk, ecnt = ref[d]
+            rows, r0 = [], 0
+            for e, c in enumerate(ecnt):
+                rows.append(ex[r0:r0 + c].float() @ w2s[d][e].float().cpu().t())
+                r0 += c
+            ys.append(torch.cat(rows) if rows else torch.zeros(0, H))
+        cref = O.combine_ref(ys, [r[2] for r in ref], [r[3] for r in ref], [x.shape[0] for x in xs])
+        for s in range(R):
+            torch.testing.assert_close(comb[s].cpu().float(), cref[s], atol=6e-2, rtol=3e-2)
+        g.check_status()
+    finally:
+        g.destroy()
+
+
+def test_buffer_without_combine_slots_pulls_and_refuses_to_push():
+    """`combine_slots=False` halves the region: the zero-copy rows are combined by the pull form,
+    a tensor outside the region cannot be combined at all, and the size hint shrinks accordingly."""
+    from gpu_data_transfer_profile_b200.parallel.buffer import Buffer
+    from gpu_data_transfer_profile_b200.parallel.symm import LocalWorld
+    T, H, E, K = 100, 512, 8, 2
+    full = Buffer.get_dispatch_config(1, T, K, E).get_nvl_buffer_size_hint(H * 2, 1)
+    half = Buffer.get_dispatch_config(1, T, K, E, combine_slots=False).get_nvl_buffer_size_hint(H * 2, 1)
+    from gpu_data_transfer_profile_b200.parallel.config import FIXED_BYTES
+    assert (half - FIXED_BYTES) < 0.6 * (full - FIXED_BYTES)          # the fixed control area aside
+    buf = Buffer(None, half, world=LocalWorld.make(1)[0], timeout_s=2.0, combine_slots=False)
+    try:
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        idx, w = O.make_routing(T, E, K, 3)
+        idx, w = idx.cuda(), w.cuda()
+        pr, _, pe, inr, _ = buf.get_dispatch_layout(idx, E)
+        rx, _, _, _, h, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, is_token_in_rank=inr,
+                                         num_tokens_per_expert=pe, zero_copy=True)
+        out, _, _ = buf.combine(rx, h)
+        torch.testing.assert_close(out.float(), x.float())
+        with pytest.raises(ValueError):
+            buf.combine(rx.clone(), h)
+        buf.check_status()
+    finally:
+        buf.destroy()

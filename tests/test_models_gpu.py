@@ -108,3 +108,29 @@ def test_moe_layer_tcgen05_experts_bf16(fused):
         torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=5e-2)
     finally:
         A.release_buffers()
+
+
+def test_moe_layer_fp8_inference_path_close_to_bf16():
+    """fp8 dispatch (cast fused into the send kernel) feeding the block-scaled fp8 fc1 directly,
+    against the same layer's bf16 path: the difference is the e4m3 rounding of rows and weights."""
+    from gpu_data_transfer_profile_b200.models import fused_a2a as A
+    from gpu_data_transfer_profile_b200.models.moe_layer import MoELayer
+    from gpu_data_transfer_profile_b200.parallel.symm import LocalWorld
+    torch.manual_seed(0)
+    T, H, F, E, K = 300, 512, 1024, 4, 2
+    world = LocalWorld.make(1)[0]
+    A.configure_buffer(num_max_tokens_per_rank=512, num_topk=K, num_experts=E, group_by_expert=True)
+    try:
+        layer = MoELayer(H, F, E, K, None, dtype=torch.bfloat16, activation="swiglu", expert_backend="tcgen05",
+                         dispatcher_mode="fused", world=world, use_fp8=True, fuse_combine=False)
+        assert layer.use_fp8
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        logits = torch.randn(T, E, device="cuda")
+        with torch.no_grad():
+            out8 = layer(x, logits)
+            layer.use_fp8 = False
+            out16 = layer(x, logits)
+        scale = float(out16.float().abs().max())
+        torch.testing.assert_close(out8.float(), out16.float(), atol=0.06 * scale, rtol=0.1)
+    finally:
+        A.release_buffers()
