@@ -106,8 +106,12 @@ notify_send_kernel(EpGeom g, EpRegions rg, PeerPtrs peers, const bool* __restric
     const int t = c * kChunkTokens + lane;
     const bool valid = t < g.T;
     if (MODE == 0) {
+      // all R flags of my token first (independent loads, one latency), then one ballot per rank
+      unsigned mine = 0;
+      if (valid)
+        for (int j = 0; j < R; ++j) mine |= (is_in_rank[(size_t)t * R + j] ? 1u : 0u) << j;
       for (int j = 0; j < R; ++j) {
-        const bool in = valid && is_in_rank[(size_t)t * R + j];
+        const bool in = (mine >> j) & 1u;
         const unsigned m = __ballot_sync(0xffffffffu, in);
         if (valid) item_rank[(size_t)t * J + j] = in ? __popc(m & lt) : -1;
         if (lane == 0) chunk_hist[(size_t)c * B + j] = __popc(m);

@@ -2,9 +2,16 @@
 //
 // Not exercised by the reference scripts (they only drive DeepEP's normal mode); the call
 // shapes follow upstream DeepEP's `low_latency_dispatch` / `low_latency_combine`. Design:
-//  * fixed-capacity receive layout: region [local expert][source rank][M rows], so a sender
-//    needs no count exchange before it stores; one copy per (token, expert), fp8 e4m3 with
-//    1x128 scales (or bf16), each row carrying (token, k) so the result can be returned;
+//  * rows land PACKED per local expert, in arrival order: a sender takes the next free row of
+//    expert e on the destination with one remote atomic add on that expert's counter and stores
+//    the row there (capacity R x M rows per expert, which R senders of at most M tokens cannot
+//    exceed). No count exchange, no receiver-side packing copy: the tensors that
+//    `low_latency_dispatch` returns ARE the receive region (fixed addresses, usable under graph
+//    replay). One copy per (token, expert), fp8 e4m3 with 1x128 scales (or bf16); each row carries
+//    (source rank, token, k) so the result can be returned;
+//  * the receive region is single-buffered: a rank may dispatch again only after a combine (whose
+//    completion proves that every peer has consumed its rows) or a barrier; the host inserts the
+//    barrier when two dispatches follow each other;
 //  * no host synchronisation and no host-side state per call: the call's epoch lives in device
 //    memory and is advanced by the kernel itself, regions are double-buffered by its parity,
 //    every kernel argument is constant -> the four kernels can be captured in a CUDA graph;
@@ -105,9 +112,7 @@ ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
   const LLTick tk = ll_tick_send(state, gridDim.x);
   const int epoch = tk.epoch;
   const int par = epoch & 1;
-  int* send_cnt = send_cnt_all + par * P.E;            // slot counters of this epoch (zero on entry)
-  if (blockIdx.x == 0)                                   // ... and clear the other set for the next call
-    for (int e = threadIdx.x; e < P.E; e += kLLThreads) send_cnt_all[(par ^ 1) * P.E + e] = 0;
+  (void)send_cnt_all;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kLLThreads / 32;
   const int row_bytes = P.fp8 ? P.H : P.H * 2;
   const int scale_cols = P.H / 128;
@@ -118,17 +123,19 @@ ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
       const long long e = topk_idx[(size_t)t * P.K + threadIdx.x];
       int given = -1;
       if (e >= 0 && e < P.E) {
-        const int slot = atomicAdd(&send_cnt[e], 1);
-        if (slot < P.M) {
-          given = slot;
-          const int d = (int)e / P.El, el = (int)e % P.El;
-          const size_t row = ((size_t)el * P.R + P.rank) * P.M + slot;
-          char* pb = peers.base[d];
-          reinterpret_cast<int*>(pb + P.recv_src[par])[row] = (t << 5) | (int)threadIdx.x;
-          reinterpret_cast<int*>(pb + P.recv_tag[par])[row] = epoch;      // marks the slot as written in this epoch
+        const int d = (int)e / P.El, el = (int)e % P.El;
+        char* pb = peers.base[d];
+        // next free row of local expert `el` on rank d (rows of one expert are packed in arrival order)
+        unsigned int* ctr = reinterpret_cast<unsigned int*>(pb + P.count[par]) + el;
+        unsigned int slot;
+        asm volatile("atom.add.relaxed.sys.global.u32 %0, [%1], 1;" : "=r"(slot) : "l"(ctr) : "memory");
+        if (slot < (unsigned int)(P.R * P.M)) {
+          given = (int)slot;
+          const size_t row = (size_t)el * P.R * P.M + slot;
+          reinterpret_cast<int*>(pb + P.recv_src[0])[row] = (P.rank << 24) | (t << 5) | (int)threadIdx.x;
           const int i = atomicAdd(&s_n, 1);
-          s_dst[i] = pb + P.recv_x[par] + row * row_bytes;
-          s_scl[i] = reinterpret_cast<float*>(pb + P.recv_scales[par]) + row * scale_cols;
+          s_dst[i] = pb + P.recv_x[0] + row * row_bytes;
+          s_scl[i] = reinterpret_cast<float*>(pb + P.recv_scales[0]) + row * scale_cols;
         } else {
           set_status(status, kOverflowRecv);
         }
@@ -188,82 +195,28 @@ ll_dispatch_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
 }
 
 // ---------------------------------------------------------------------------------------
-// dispatch, receive half: wait for every source, then pack each local expert's rows
-// contiguously: out_x[el][0..count[el]) ordered by source rank.  grid = (El, split)
+// dispatch, receive half: wait for every source's arrival, then read (and clear) the per-expert
+// row counters. One CTA; nothing is copied.
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kLLThreads)
-ll_dispatch_recv_kernel(LLParams P, char* self_base, char* __restrict__ out_x,
-                        float* __restrict__ out_scales, int* __restrict__ out_src,
-                        int* __restrict__ out_count, int2* __restrict__ out_range,
-                        int* state, int* status) {
-  __shared__ int s_off[kMaxRanks + 1];
-  __shared__ int s_cnt[kMaxRanks];
+ll_dispatch_recv_kernel(LLParams P, char* self_base, int* __restrict__ out_count, int* state, int* status) {
   __shared__ int ok;
   ll_stream_order();
   const LLTick tk = ll_tick_recv(state);
-  const int epoch = tk.epoch;
-  const int par = epoch & 1;
+  const int par = tk.epoch & 1;
   if (threadIdx.x == 0) ok = 1;
-  if (threadIdx.x < kMaxRanks) s_cnt[threadIdx.x] = 0;
   __syncthreads();
   if (threadIdx.x < P.R) {
     const int* flags = reinterpret_cast<const int*>(self_base + P.flags) + kChLLDispatch * kMaxRanks;
     if (!wait_counter_reached(flags + threadIdx.x, tk.target, P.timeout_ns, status, kTimeoutLowLatency)) ok = 0;
   }
   __syncthreads();
-  const int el = blockIdx.x;
-  if (!ok) {
-    if (threadIdx.x == 0 && blockIdx.y == 0) out_count[el] = 0;
-    return;
-  }
-  // rows of (el, source s) occupy slots 0..count-1; a slot belongs to this call iff its tag is the epoch
-  const int* tags = reinterpret_cast<const int*>(self_base + P.recv_tag[par]) + (size_t)el * P.R * P.M;
-  for (int i = threadIdx.x; i < P.R * P.M; i += kLLThreads)
-    if (__ldcg(&tags[i]) == epoch) atomicAdd(&s_cnt[i / P.M], 1);
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int s = 0; s < P.R; ++s) {
-      s_off[s] = acc;
-      int c = s_cnt[s];
-      c = c < 0 ? 0 : (c > P.M ? P.M : c);
-      if (blockIdx.y == 0) out_range[el * P.R + s] = make_int2(acc, c);
-      acc += c;
-    }
-    s_off[P.R] = acc;
-    if (blockIdx.y == 0) out_count[el] = acc;
-  }
-  __syncthreads();
-  const int total = s_off[P.R];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kLLThreads / 32;
-  const int row_bytes = P.fp8 ? P.H : P.H * 2;
-  const int scale_cols = P.H / 128;
-  const size_t cap = (size_t)P.R * P.M;
-  for (int j = blockIdx.y * nwarps + warp; j < total; j += gridDim.y * nwarps) {
-    int s = 0;
-    while (s + 1 < P.R && j >= s_off[s + 1]) ++s;
-    const size_t in_row = ((size_t)el * P.R + s) * P.M + (j - s_off[s]);
-    const size_t out_row = (size_t)el * cap + j;
-    const char* src = self_base + P.recv_x[par] + in_row * row_bytes;
-    char* dst = out_x + out_row * row_bytes;
-    const int nv = row_bytes >> 4;
-    for (int v0 = lane; v0 < nv; v0 += 32 * 16) {
-      uint4 buf[16];
-#pragma unroll
-      for (int u = 0; u < 16; ++u)
-        if (v0 + u * 32 < nv) buf[u] = ld_global_v4(src + ((size_t)(v0 + u * 32) << 4));
-#pragma unroll
-      for (int u = 0; u < 16; ++u)
-        if (v0 + u * 32 < nv) st_global_v4(dst + ((size_t)(v0 + u * 32) << 4), buf[u]);
-    }
-    if (P.fp8) {
-      const float* ss = reinterpret_cast<const float*>(self_base + P.recv_scales[par]) + in_row * scale_cols;
-      for (int c = lane; c < scale_cols; c += 32) out_scales[out_row * scale_cols + c] = ss[c];
-    }
-    if (lane == 0) {
-      const int info = reinterpret_cast<const int*>(self_base + P.recv_src[par])[in_row];
-      out_src[out_row] = (s << 24) | (info & 0xffffff);
-    }
+  int* cnt = reinterpret_cast<int*>(self_base + P.count[par]);
+  for (int el = threadIdx.x; el < P.El; el += kLLThreads) {
+    int c = ok ? __ldcg(&cnt[el]) : 0;
+    c = c < 0 ? 0 : (c > P.R * P.M ? P.R * P.M : c);
+    out_count[el] = c;
+    cnt[el] = 0;                 // this parity is used again two dispatches from now
   }
 }
 
@@ -280,17 +233,16 @@ ll_combine_send_kernel(LLParams P, PeerPtrs peers, const char* __restrict__ x,
   const int el = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kLLThreads / 32;
   const size_t cap = (size_t)P.R * P.M;
-  int total = count[el];
+  int total = __ldcg(&count[el]);
   total = total < 0 ? 0 : (total > (int)cap ? (int)cap : total);
   const int row_bytes = P.H * 2;
-  // rows of one expert are packed by source rank: give every warp a contiguous slice so that the
-  // warps running at one time address all source ranks, not one after the other
+  // rows of one expert arrive interleaved from all source ranks: every warp takes a contiguous slice
   const int nslices = gridDim.y * nwarps;
   const int per = (total + nslices - 1) / nslices;
   const int j0 = (blockIdx.y * nwarps + warp) * per;
   const int j1 = min(total, j0 + per);
   for (int j = j0; j < j1; ++j) {
-    const int info = src_info[(size_t)el * cap + j];
+    const int info = __ldcg(&src_info[(size_t)el * cap + j]);
     const int s = (info >> 24) & 0xff, t = (info & 0xffffff) >> 5, k = info & 31;
     if (s >= P.R || t >= P.M || k >= P.K) {
       if (lane == 0) set_status(status, kOverflowSlots);
@@ -379,8 +331,7 @@ constexpr int kPullGroup = 4;    // contributors whose loads are in flight toget
 constexpr int kPullUnroll = 4;   // 16-byte vectors per lane and contributor
 
 __global__ void __launch_bounds__(kLLThreads)
-ll_combine_pull_kernel(LLParams P, PeerPtrs peers, int phase, const int* __restrict__ range,
-                       const int* __restrict__ send_slot, const long long* __restrict__ topk_idx,
+ll_combine_pull_kernel(LLParams P, PeerPtrs peers, int phase, const int* __restrict__ send_slot, const long long* __restrict__ topk_idx,
                        const float* __restrict__ topk_w, char* __restrict__ out, int* state, int* status) {
   __shared__ int s_epoch;
   __shared__ unsigned int s_target;
@@ -400,17 +351,11 @@ ll_combine_pull_kernel(LLParams P, PeerPtrs peers, int phase, const int* __restr
     s_ok = 1;
   }
   __syncthreads();
-  const int epoch = s_epoch, par = epoch & 1;
+  const int epoch = s_epoch;
   const unsigned int target = s_target;
   char* self_base = peers.base[P.rank];
   if (phase != 2 && blockIdx.x == 0) {
-    // tell every source rank where, in my packed expert rows, its rows start
-    for (int i = threadIdx.x; i < P.R * P.El; i += blockDim.x) {
-      const int s = i / P.El, el = i % P.El;
-      int* dst = reinterpret_cast<int*>(peers.base[s] + P.range_tab[par]) + P.rank * P.El + el;
-      st_relaxed_sys(dst, range[((size_t)el * P.R + s) * 2]);
-    }
-    __syncthreads();
+    // announce: my expert output (written by earlier kernels of this stream) may be read
     if ((int)threadIdx.x < P.R) {
       unsigned int* ctr = reinterpret_cast<unsigned int*>(peers.base[threadIdx.x] + P.flags) + kChLLPull * kMaxRanks + P.rank;
       asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ctr), "r"(1u) : "memory");
@@ -429,7 +374,6 @@ ll_combine_pull_kernel(LLParams P, PeerPtrs peers, int phase, const int* __restr
     int parts = (nvec + 32 * kPullUnroll - 1) / (32 * kPullUnroll);   // one batch of loads per warp and contributor
     if (parts < 1) parts = 1;
     const int part_vec = (nvec + parts - 1) / parts;
-    const int* rtab = reinterpret_cast<const int*>(self_base + P.range_tab[par]);
     const size_t cap = (size_t)P.R * P.M;
     const int items = P.T * parts;
     for (int it = blockIdx.x * nwarps + warp; it < items; it += gridDim.x * nwarps) {
@@ -450,15 +394,12 @@ ll_combine_pull_kernel(LLParams P, PeerPtrs peers, int phase, const int* __restr
           if (k >= P.K) continue;
           const long long e = topk_idx[(size_t)t * P.K + k];
           const int slot = send_slot[(size_t)t * P.K + k];
-          if (e < 0 || e >= P.E || slot < 0 || slot >= P.M) continue;
+          if (e < 0 || e >= P.E || slot < 0) continue;
           const int d = (int)e / P.El, el = (int)e % P.El;
-          const int start = __ldcg(&rtab[d * P.El + el]);
-          if (start < 0 || (size_t)start + slot >= cap) {
-            if (lane == 0) set_status(status, kOverflowSlots);
-            continue;
-          }
+          if ((size_t)slot >= cap) continue;
           wk[g] = topk_w ? topk_w[(size_t)t * P.K + k] : 1.f;
-          const char* rowp = peers.base[d] + P.comb_in + ((size_t)el * cap + start + slot) * row_bytes;
+          // the row that dispatch stored for (t, k): packed row `slot` of local expert el on rank d
+          const char* rowp = peers.base[d] + P.comb_in + ((size_t)el * cap + slot) * row_bytes;
 #pragma unroll
           for (int u = 0; u < kPullUnroll; ++u) {
             const int v = v_lo + u * 32 + lane;
@@ -530,12 +471,9 @@ void launch_ll_dispatch_send(const LLParams& P, const PeerPtrs& peers, const cha
   ll_launch(ll_dispatch_send_kernel, dim3(P.G), P.pdl != 0, st, P, peers, x, topk_idx, send_cnt, state, status,
             send_slot);
 }
-void launch_ll_dispatch_recv(const LLParams& P, char* self_base, char* out_x, float* out_scales,
-                             int* out_src, int* out_count, int* out_range, int* state,
-                             int* status, int split, cudaStream_t st) {
-  if (split < 1) split = 1;
-  ll_launch(ll_dispatch_recv_kernel, dim3(P.El, split), P.pdl != 0, st, P, self_base, out_x, out_scales, out_src,
-            out_count, reinterpret_cast<int2*>(out_range), state, status);
+void launch_ll_dispatch_recv(const LLParams& P, char* self_base, int* out_count, int* state, int* status,
+                             cudaStream_t st) {
+  ll_launch(ll_dispatch_recv_kernel, dim3(1), P.pdl != 0, st, P, self_base, out_count, state, status);
 }
 void launch_ll_combine_send(const LLParams& P, const PeerPtrs& peers, const char* x, const int* src_info,
                             const int* count, int* state, int* status, cudaStream_t st) {
@@ -549,11 +487,11 @@ void launch_ll_combine_recv(const LLParams& P, char* self_base, const long long*
   ll_launch(ll_combine_recv_kernel, dim3(g), P.pdl != 0, st, P, self_base, topk_idx, topk_w, out, state, status);
 }
 
-void launch_ll_combine_pull(const LLParams& P, const PeerPtrs& peers, int phase, const int* range,
-                            const int* send_slot, const long long* topk_idx, const float* topk_w,
-                            char* out, int* state, int* status, cudaStream_t st) {
-  ll_launch(ll_combine_pull_kernel, dim3(phase == 1 ? 1 : P.G), P.pdl != 0, st, P, peers, phase, range,
-            send_slot, topk_idx, topk_w, out, state, status);
+void launch_ll_combine_pull(const LLParams& P, const PeerPtrs& peers, int phase, const int* send_slot,
+                            const long long* topk_idx, const float* topk_w, char* out, int* state,
+                            int* status, cudaStream_t st) {
+  ll_launch(ll_combine_pull_kernel, dim3(phase == 1 ? 1 : P.G), P.pdl != 0, st, P, peers, phase, send_slot,
+            topk_idx, topk_w, out, state, status);
 }
 
 }  // namespace b200ep

@@ -780,13 +780,13 @@ class Buffer:
             carve = _LLCarve(self.num_nvl_bytes, self.group_size, E, M, H, K)
             dev = self.device
             if reuse:
-                # the region held other data: every rank drains, clears its slot tags (a stale word
-                # must never look like a current epoch), and only then may anyone send again
+                # the region held other data: every rank drains, clears its per-expert row counters
+                # (they must start at zero), and only then may anyone send again
                 self.barrier()
-                rows = (E // self.group_size) * self.group_size * M
-                for off in carve.recv_tag:
-                    self.region.view(off, (rows,), "int32").zero_()
+                for off in carve.count:
+                    self.region.view(off, (E // self.group_size,), "int32").zero_()
                 self.barrier()
+            self._ll_dispatch_pending = False
             if self._ll_words is None:
                 # device-resident op state (epochs and arrival targets); lives as long as the buffer
                 # because the peers' arrival counters are cumulative
@@ -818,36 +818,42 @@ class Buffer:
         topk_idx = topk_idx.to(torch.int64).contiguous()
         K = topk_idx.shape[1]
         st = self._ll_state(E, K, H, M)
+        if getattr(self, "_ll_dispatch_pending", False):
+            # The receive region is single-buffered: a second dispatch may only overwrite it once every
+            # peer has consumed the previous one. A combine in between proves that; without one, drain.
+            self.barrier()
+        self._ll_dispatch_pending = True
         pv = self._ll_params(st, T, use_fp8)
         self.C.ll_dispatch_send(pv, self.peers, x, topk_idx, st["send_cnt"], st["words"][0:6], self.status_ptr,
                                 st["send_slot"])
         return dict(st=st, pv=pv, T=T, H=H, K=K, E=E, M=M, fp8=use_fp8, topk_idx=topk_idx, x=x)
 
     def _ll_dispatch_recv(self, d):
+        """Count-only: the rows already lie packed per local expert in the receive region, which is
+        what the returned tensors are views of (fixed addresses; valid until the next dispatch)."""
         R, El, M, H = self.group_size, d["E"] // self.group_size, d["M"], d["H"]
-        dev = self.device
+        c = d["st"]["carve"]
         rows = R * M
+        out_count = torch.empty((El,), dtype=torch.int32, device=self.device)
+        self.C.ll_dispatch_recv(d["pv"], self.region.local_ptr, out_count, d["st"]["words"][0:6], self.status_ptr)
         if d["fp8"]:
-            out_x = torch.empty((El, rows, H), dtype=torch.float8_e4m3fn, device=dev)
-            out_s = torch.empty((El, rows, H // 128), dtype=torch.float32, device=dev)
+            out_x = (self.region.view(c.recv_x[0], (El, rows, H), "float8_e4m3fn"),
+                     self.region.view(c.recv_scales[0], (El, rows, H // 128), "float32"))
         else:
-            out_x = torch.empty((El, rows, H), dtype=torch.bfloat16, device=dev)
-            out_s = None
-        out_src = torch.empty((El, rows), dtype=torch.int32, device=dev)
-        out_count = torch.empty((El,), dtype=torch.int32, device=dev)
-        out_range = torch.empty((El, R, 2), dtype=torch.int32, device=dev)
-        self.C.ll_dispatch_recv(d["pv"], self.region.local_ptr, out_x, out_s, out_src, out_count, out_range,
-                                d["st"]["words"][0:6], self.status_ptr, 4)
-        handle = (out_src, out_range, M, H, d["E"], out_count, d["K"])
-        return ((out_x, out_s) if d["fp8"] else out_x), out_count, handle
+            out_x = self.region.view(c.recv_x[0], (El, rows, H), "bfloat16")
+        out_src = self.region.view(c.recv_src[0], (El, rows), "int32")
+        handle = (out_src, None, M, H, d["E"], out_count, d["K"])
+        return out_x, out_count, handle
 
     @_nvtx("b200ep.ll_dispatch")
     def low_latency_dispatch(self, x, topk_idx, num_max_dispatch_tokens_per_rank: int, num_experts: int,
                              use_fp8: bool = True, async_finish: bool = False,
                              return_recv_hook: bool = False):
         """-> (recv_x [E_local, R*M, H] | (fp8, scales), recv_count [E_local] i32, handle, event, hook).
-        The first recv_count[e] rows of expert e are valid. No host synchronisation; may be
-        captured in a CUDA graph. With return_recv_hook=True only the send half is launched and
+        The first recv_count[e] rows of expert e are valid (in arrival order; `handle[0]` gives
+        (source rank << 24 | token << 5 | k) per row). The tensors are views of the receive region:
+        fixed addresses, valid until the next low_latency_dispatch on this buffer. No host
+        synchronisation; may be captured in a CUDA graph. With return_recv_hook=True only the send half is launched and
         the returned hook launches the receive half (then fills the same tensors)."""
         compute = self._enter(None, False, False)
         with torch.cuda.stream(self.comm_stream):
@@ -878,7 +884,9 @@ class Buffer:
         return self.region.view(st["carve"].comb_in, (El, self.group_size * M, H), "bfloat16")
 
     def _ll_combine_pull(self, phase: int, topk_idx, topk_weights, handle, out=None):
-        _src, rng, M, H, E, _count, K = handle
+        _src, _rng, M, H, E, _count, K = handle
+        if phase != 2:
+            self._ll_dispatch_pending = False
         st = self._ll_state(E, K, H, M)
         topk_idx = topk_idx.to(torch.int64).contiguous()
         T = topk_idx.shape[0]
@@ -886,7 +894,7 @@ class Buffer:
         if out is None:
             out = torch.empty((T, H), dtype=torch.bfloat16, device=self.device)
         w = topk_weights.to(torch.float32).contiguous() if topk_weights is not None else None
-        self.C.ll_combine_pull(pv, self.peers, phase, rng, st["send_slot"], topk_idx, w, out,
+        self.C.ll_combine_pull(pv, self.peers, phase, st["send_slot"], topk_idx, w, out,
                                st["words"][12:18], self.status_ptr)
         return out
 
@@ -901,6 +909,7 @@ class Buffer:
         if x.dtype != torch.bfloat16 or not x.is_contiguous():
             raise ValueError("low-latency combine takes a contiguous bf16 [E_local, R*M, hidden] tensor")
         pv = self._ll_params(st, 0, False)
+        self._ll_dispatch_pending = False
         self.C.ll_combine_send(pv, self.peers, x, src_info, count, st["words"][6:12], self.status_ptr)
         return dict(st=st, H=H)
 
@@ -944,7 +953,9 @@ class Buffer:
 
 
 class _LLCarve:
-    """Region offsets of low-latency mode (both epoch parities)."""
+    """Region offsets of low-latency mode. Every region is laid out twice (index 0 / 1); the receive
+    rows, scales and source words use copy 0 only (single-buffered, see csrc/ep/ll.cu), the
+    push-combine slots alternate by epoch parity."""
 
     @staticmethod
     def _sizes(R, E, M, H, K):
