@@ -1,18 +1,48 @@
 """Profiling driver: runs the two sweeps of the reference's `Copy_Engine/sample_run.sh:4-32`
 (fan-out copy 1-10 MiB; address layouts 8K-2048K) and wraps every run in Nsight Systems with the
 reference's options (`-s none --cpuctxsw=none --trace=cuda,nvtx --gpu-metrics-devices=0
---gpu-metrics-frequency=10000`) when the `nsys` CLI exists. Without nsys the runs still execute
-and append their JSONL records, so the sweep is usable on machines that only have `ncu`.
+--gpu-metrics-frequency=10000`) when the `nsys` CLI exists (`--tool nsys`, the default when it is
+found). `--tool ncu` is the path for machines that only have Nsight Compute: every run is wrapped
+in a ONE-PASS launch list (`ncu --metrics gpu__time_duration.sum --clock-control none --csv`),
+which is only done for single-process runs (`--gpus 1`; a multi-rank command is never put under
+ncu), and the launch list is reduced to per-kernel count / total / mean microseconds in
+`<out>/<name>.kernels.json`. `--tool none` just runs the sweeps and appends their JSONL records.
 
     python -m gpu_data_transfer_profile_b200.bench.profile_sweep --gpus 8 --out results/
+    python -m gpu_data_transfer_profile_b200.bench.profile_sweep --gpus 1 --tool ncu --only a2a_batch_1M --out results/
 """
 from __future__ import annotations
 
 import argparse
+import csv
+import json
 import os
 import shutil
 import subprocess
 import sys
+
+
+def summarize_launch_list(path: str) -> dict:
+    """`ncu --csv --metrics gpu__time_duration.sum` log -> {kernel: {launches, total_us, mean_us}}."""
+    with open(path, newline="") as f:
+        lines = [l for l in f if l.startswith('"')]
+    out = {}
+    for r in csv.DictReader(lines):
+        if r.get("Metric Name") != "gpu__time_duration.sum":
+            continue
+        try:
+            ns = float(r["Metric Value"].replace(",", ""))
+        except (KeyError, ValueError):
+            continue
+        unit = r.get("Metric Unit", "ns")
+        us = ns * {"ns": 1e-3, "us": 1.0, "ms": 1e3, "s": 1e6}.get(unit, 1e-3)
+        name = r.get("Kernel Name", "?").split("(")[0]
+        d = out.setdefault(name, dict(launches=0, total_us=0.0))
+        d["launches"] += 1
+        d["total_us"] += us
+    for d in out.values():
+        d["mean_us"] = d["total_us"] / d["launches"]
+    return out
 
 
 def commands(gpus: int, out: str, iters: int, warmup: int):
@@ -39,14 +69,38 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--gpu-metrics-set", default=None, help="e.g. gb100; omitted when not given")
+    ap.add_argument("--tool", choices=("auto", "nsys", "ncu", "none"), default="auto",
+                    help="auto: nsys when installed, else none")
     ap.add_argument("--dry-run", action="store_true", help="print the command lines only")
     ap.add_argument("--only", default="", help="substring filter on the run name")
     a = ap.parse_args()
     os.makedirs(a.out, exist_ok=True)
-    nsys = shutil.which("nsys")
+    nsys = shutil.which("nsys") if a.tool in ("auto", "nsys") else None
+    if a.tool == "nsys" and not nsys:
+        print("nsys is not installed; use --tool ncu or --tool none", file=sys.stderr)
+        return 2
+    ncu = shutil.which("ncu") if a.tool == "ncu" else None
+    if a.tool == "ncu" and (not ncu or a.gpus != 1):
+        print("--tool ncu needs the ncu CLI and --gpus 1 (a multi-rank command is never put under ncu)", file=sys.stderr)
+        return 2
     rc = 0
     for name, cmd in commands(a.gpus, a.out, a.iters, a.warmup):
         if a.only and a.only not in name:
+            continue
+        if ncu:
+            # single rank: run the module directly (no launcher process between ncu and the kernels)
+            cmd = [sys.executable] + cmd[cmd.index("-m", 2):]
+            log = os.path.join(a.out, name + ".launches.csv")
+            print(("[dry-run] " if a.dry_run else "[run] ") + " ".join(cmd), flush=True)
+            if not a.dry_run:
+                plain = subprocess.run(cmd).returncode          # must succeed without the profiler first
+                rc |= plain
+                if plain == 0:
+                    prof = [ncu, "--metrics", "gpu__time_duration.sum", "--clock-control", "none", "--csv", "--log-file", log]
+                    rc |= subprocess.run(prof + cmd).returncode
+                    if os.path.exists(log):
+                        with open(os.path.join(a.out, name + ".kernels.json"), "w") as f:
+                            json.dump(summarize_launch_list(log), f, indent=1)
             continue
         if nsys:
             prof = [nsys, "profile", "-s", "none", "--cpuctxsw=none", "--trace=cuda,nvtx", "--gpu-metrics-devices=0",

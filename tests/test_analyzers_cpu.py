@@ -138,3 +138,30 @@ def test_ncu_raw_summary(tmp_path):
     rows = ncu_summary.summarize(ncu_summary.read_raw(str(p)), "grouped_gemm", flops=2.4e12, peaks={"bf16_tflops": 1600.0, "hbm_gbs": 6500.0})
     assert len(rows) == 1 and rows[0]["tflops"] == pytest.approx(1200.0)
     assert rows[0]["dram_gb_s"] == pytest.approx(750.0) and rows[0]["frac_of_measured_bf16_peak"] == pytest.approx(0.75)
+
+
+def test_profile_sweep_reduces_an_ncu_launch_list(tmp_path):
+    """The ncu path of the profiling driver: a one-pass launch list becomes per-kernel totals."""
+    from gpu_data_transfer_profile_b200.bench.profile_sweep import summarize_launch_list
+    log = tmp_path / "run.launches.csv"
+    log.write_text(
+        '==PROF== Connected to process 1\n'
+        '"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size","Grid Size","Device","CC","Section Name","Metric Name","Metric Unit","Metric Value"\n'
+        '"0","1","python","h","b200ep::batched_copy_kernel(const CopyDesc *, int)","1","7","(256, 1, 1)","(8, 7, 1)","0","10.0","Command line profiler metrics","gpu__time_duration.sum","ns","12,000"\n'
+        '"1","1","python","h","b200ep::batched_copy_kernel(const CopyDesc *, int)","1","7","(256, 1, 1)","(8, 7, 1)","0","10.0","Command line profiler metrics","gpu__time_duration.sum","ns","8,000"\n'
+        '"2","1","python","h","void at::fill_kernel<int>(int)","1","7","(256, 1, 1)","(8, 1, 1)","0","10.0","Command line profiler metrics","gpu__time_duration.sum","us","3.5"\n')
+    res = summarize_launch_list(str(log))
+    k = res["b200ep::batched_copy_kernel"]
+    assert k["launches"] == 2 and abs(k["total_us"] - 20.0) < 1e-9 and abs(k["mean_us"] - 10.0) < 1e-9
+    assert abs(res["void at::fill_kernel<int>"]["total_us"] - 3.5) < 1e-9
+
+
+def test_profile_sweep_dry_run_with_ncu_tool_refuses_multi_rank(capsys):
+    import sys
+    from gpu_data_transfer_profile_b200.bench import profile_sweep as P
+    argv = sys.argv
+    try:
+        sys.argv = ["profile_sweep", "--gpus", "8", "--tool", "ncu", "--dry-run", "--out", "/tmp/_ps_out"]
+        assert P.main() == 2
+    finally:
+        sys.argv = argv

@@ -128,3 +128,18 @@ def test_lsu_copy_overlapping_launches():
     K.lsu_copy(dst, src, n, ctas=16, threads=512, launches=5, overlap_launches=True)
     torch.cuda.synchronize()
     assert torch.equal(dst, src)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs in one process")
+def test_nvlink_packet_probe_single_process_two_gpus():
+    """The probe that is profiled with the NVLink counters: one process pushes from GPU 0 to GPU 1."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "gpu_data_transfer_profile_b200.bench.nvlink_packet_probe", "--nbytes", "4M"],
+                       cwd=root, capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    rec = json.loads(r.stdout.strip().splitlines()[-1])
+    assert rec["check"] and rec["lsu16_gbs"] > 0 and rec["copy_engine_gbs"] > 0
