@@ -69,7 +69,8 @@ struct WgradParams {
   int* status;
 };
 // g: bf16 [rows, M], x: bf16 [rows, N], both on this GPU, rows grouped by local expert.
-// pair: CTA pairs on 256 x 256 tiles of dW (M % 256 == 0) instead of single CTAs on 128 x 256 (M % 128 == 0).
+// pair: CTA pairs on 256 x 256 tiles of dW (M % 256 == 0) instead of single CTAs on 128 x 256 (M % 8 == 0; a
+// last tile that hangs over M reads zeros and stores only the rows below M).
 int launch_grouped_wgrad(const void* g, const void* x, long long rows, WgradParams p, int ctas, bool pair,
                          cudaStream_t st);
 

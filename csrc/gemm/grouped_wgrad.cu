@@ -88,7 +88,7 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
   const bool leader = cta_rank == 0;
   const int unit = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int n_units = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
-  const int m_tiles = p.M / TM, n_tiles = (p.N + BN - 1) / BN;
+  const int m_tiles = (p.M + TM - 1) / TM, n_tiles = (p.N + BN - 1) / BN;   // a last m-tile may hang over M: its G columns read as zeros, its dW rows are not stored
   const int gm = max(1, BAND_M_TILES_ROWS / TM);
 
   if (threadIdx.x == 0) {
@@ -276,7 +276,7 @@ grouped_wgrad_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
         for (int step = 0; step < 8; ++step) {
           const int r = step * 4 + (lane >> 3);
           const int seg = lane & 7;
-          if (col0 + seg * 8 < p.N) {
+          if (col0 + seg * 8 < p.N && row_base + r < p.M) {
             const uint4 val = *reinterpret_cast<const uint4*>(my_smem + r * EPI_ROW_BYTES + seg * 16);
             st_global_v4(reinterpret_cast<char*>(out_e + (size_t)(row_base + r) * p.N + col0 + seg * 8), val);
           }
@@ -338,7 +338,8 @@ static int launch(const CUtensorMap& mg, const CUtensorMap& mx, const WgradParam
 int launch_grouped_wgrad(const void* g, const void* x, long long rows, WgradParams p, int ctas, bool pair,
                          cudaStream_t st) {
   const int tm = pair ? 256 : 128;
-  if (p.El < 1 || p.El > wg::kMaxLocalExperts || p.M <= 0 || p.M % tm || p.N <= 0 || p.N % 8) return 1;
+  // pairs split a 256-row tile of dW between two CTAs: M % 256; a single CTA masks a ragged last tile: M % 8
+  if (p.El < 1 || p.El > wg::kMaxLocalExperts || p.M <= 0 || (pair ? p.M % tm : p.M % 8) || p.N <= 0 || p.N % 8) return 1;
   if (reinterpret_cast<uintptr_t>(g) % 16 || reinterpret_cast<uintptr_t>(x) % 16 || rows < 1) return 1;
   CUtensorMap mg, mx;
   if (make_tmap_bf16(&mg, g, rows, p.M, 64, wg::BK)) return 3;

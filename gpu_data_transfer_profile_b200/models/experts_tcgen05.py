@@ -18,9 +18,10 @@ from .experts import GroupedExpertsBase
 
 
 def _wgrad(dy, a, counts, out_shape, expert_off=None):
-    """dW[e] = dy_e^T @ a_e per local expert: the tcgen05 ragged-reduction kernel when the shapes
-    allow it (dW rows a multiple of 128), else a library GEMM per expert."""
-    if expert_off is not None and out_shape[1] % 128 == 0 and out_shape[2] % 8 == 0 and dy.shape[0] > 0:
+    """dW[e] = dy_e^T @ a_e per local expert on the tcgen05 ragged-reduction kernel (dW rows and
+    columns multiples of 8, which the constructor guarantees); a library GEMM per expert only when
+    no device-side offsets were given or there are no rows at all."""
+    if expert_off is not None and out_shape[1] % 8 == 0 and out_shape[2] % 8 == 0 and dy.shape[0] > 0:
         return G.grouped_wgrad(dy.contiguous(), a.contiguous(), expert_off)
     dw = torch.zeros(out_shape, dtype=dy.dtype, device=dy.device)
     r = 0

@@ -86,7 +86,7 @@ def grouped_gemm_combine(a: torch.Tensor, w: torch.Tensor, expert_off: torch.Ten
 def grouped_wgrad(g: torch.Tensor, x: torch.Tensor, expert_off: torch.Tensor, *, out: Optional[torch.Tensor] = None,
                   ctas: int = 0, pair: Optional[bool] = None) -> torch.Tensor:
     """dW[e] = g_e.T @ x_e over the rows of local expert e (g bf16 [rows,M], x bf16 [rows,N]) -> bf16 [E,M,N].
-    Both operands are read as stored; an expert without rows gets zeros. M % 128 == 0 (the pair form
+    Both operands are read as stored; an expert without rows gets zeros. M % 8 == 0 (the pair form
     needs M % 256 == 0 and is skipped otherwise), N % 8 == 0."""
     E = expert_off.numel() - 1
     if out is None:

@@ -68,6 +68,7 @@ def test_grouped_gemm_swiglu_prob(counts, F, K, pair):
 
 @pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("counts,M,N", [([64], 256, 256), ([128, 192], 256, 512), ([100, 0, 333, 7], 256, 320),
+                                        ([90, 40], 192, 256), ([70, 0, 130], 200, 136),
                                         ([1], 512, 64), ([513, 63, 65], 768, 264), ([0, 0, 40], 256, 128),
                                         ([1000, 129, 2300], 512, 1024)])
 def test_grouped_wgrad(counts, M, N, pair):
