@@ -10,7 +10,20 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// cuTensorMapEncodeTiled is a DRIVER entry point: it needs a CUDA context that is current on the
+// calling thread. The runtime binds the primary context to a thread lazily, on the first runtime
+// call that needs it, and worker threads (autograd's backward threads, any user thread) may reach
+// the grouped GEMM launchers before they have made one: the encode then fails or crashes.
+// cudaSetDevice on the thread's current device binds the context; done once per thread.
+inline void tmap_bind_context_to_this_thread() {
+  static thread_local bool bound = false;
+  if (bound) return;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) bound = true;
+}
+
 inline EncodeTiledFn tmap_encode_fn() {
+  tmap_bind_context_to_this_thread();
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* sym = nullptr;

@@ -263,3 +263,43 @@ def test_tcgen05_experts_consume_fp8_dispatch_rows():
     y = mod((xq, xs), counts, p)
     y_ref = mod(x, counts, p)                              # bf16 path on the unquantised rows
     torch.testing.assert_close(y.float(), y_ref.detach().float(), atol=0.08 * float(y_ref.detach().float().abs().max()), rtol=0.1)
+
+
+def test_grouped_gemms_work_from_a_fresh_thread():
+    """The launchers encode TMA descriptors through a driver entry point, which needs a context
+    bound to the calling thread; a thread that has made no CUDA runtime call yet (autograd's
+    backward workers, user threads) must get one bound by the launcher itself."""
+    import threading
+    from gpu_data_transfer_profile_b200.ops import gemm as G
+    torch.manual_seed(0)
+    counts = [70, 0, 130]
+    rows, K, N = sum(counts), 256, 384
+    off = G.offsets_from_counts(counts, "cuda")
+    a = torch.randn(rows, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(len(counts), N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    g = torch.randn(rows, N, device="cuda").to(torch.bfloat16)
+    out, dx, dw = (torch.empty(rows, N, dtype=torch.bfloat16, device="cuda"),
+                   torch.empty(rows, K, dtype=torch.bfloat16, device="cuda"),
+                   torch.empty(len(counts), N, K, dtype=torch.bfloat16, device="cuda"))
+    torch.cuda.synchronize()
+    err = []
+
+    def work():                                    # first CUDA work of this thread
+        try:
+            G.grouped_gemm(a, w, off, out=out)
+            G.grouped_gemm(g, w, off, out=dx, w_kn=True)
+            G.grouped_wgrad(g, a, off, out=dw)
+            torch.cuda.synchronize()
+        except Exception as e:                     # noqa: BLE001
+            err.append(e)
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    assert not err, err
+    r = 0
+    for e, c in enumerate(counts):
+        if c:
+            torch.testing.assert_close(out[r:r + c].float(), a[r:r + c].float() @ w[e].float().t(), atol=3e-2, rtol=3e-2)
+            torch.testing.assert_close(dx[r:r + c].float(), g[r:r + c].float() @ w[e].float(), atol=3e-2, rtol=3e-2)
+        r += c
