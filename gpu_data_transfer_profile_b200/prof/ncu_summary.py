@@ -22,12 +22,29 @@ WANTED = ("gpu__time_duration.sum", "dram__bytes_read.sum", "dram__bytes_write.s
           "lts__t_bytes.sum", "l1tex__t_bytes.sum", "launch__shared_mem_per_block_dynamic")
 
 
+_UNIT_SCALE = {"ns": 1.0, "us": 1e3, "ms": 1e6, "s": 1e9,                       # times -> ns
+               "byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9, "Tbyte": 1e12}  # sizes -> bytes
+
+
 def read_raw(path: str) -> List[Dict[str, str]]:
-    """Rows of the raw page: one dict per profiled launch (the units row is dropped)."""
+    """Rows of the raw page: one dict per profiled launch. The page's second row gives each
+    column's unit (ncu picks us/ms and Kbyte/Mbyte per column); times are rescaled to ns and
+    sizes to bytes, so every consumer sees one unit."""
     with open(path, newline="") as f:
         lines = [l for l in f if l.startswith('"')]
     rows = list(csv.DictReader(lines))
-    return [r for r in rows if r.get("ID", "").strip().isdigit()]
+    units = next((r for r in rows if not r.get("ID", "").strip().isdigit()), {})
+    out = []
+    for r in rows:
+        if not r.get("ID", "").strip().isdigit():
+            continue
+        for k, u in units.items():
+            scale = _UNIT_SCALE.get((u or "").strip())
+            v = _num(r.get(k))
+            if scale is not None and scale != 1.0 and v is not None:
+                r[k] = repr(v * scale)
+        out.append(r)
+    return out
 
 
 def _num(v: str):

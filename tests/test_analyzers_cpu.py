@@ -138,6 +138,11 @@ def test_ncu_raw_summary(tmp_path):
     rows = ncu_summary.summarize(ncu_summary.read_raw(str(p)), "grouped_gemm", flops=2.4e12, peaks={"bf16_tflops": 1600.0, "hbm_gbs": 6500.0})
     assert len(rows) == 1 and rows[0]["tflops"] == pytest.approx(1200.0)
     assert rows[0]["dram_gb_s"] == pytest.approx(750.0) and rows[0]["frac_of_measured_bf16_peak"] == pytest.approx(0.75)
+    # ncu chooses the unit per column: the same launch reported in ms and Mbyte reads the same
+    p.write_text('"ID","Kernel Name","gpu__time_duration.sum","dram__bytes_read.sum","dram__bytes_write.sum"\n'
+                 '"","","ms","Gbyte","Mbyte"\n"0","grouped_gemm_kernel<1>","2.0","1.0","500"\n')
+    rows = ncu_summary.summarize(ncu_summary.read_raw(str(p)), "grouped_gemm", flops=2.4e12)
+    assert rows[0]["tflops"] == pytest.approx(1200.0) and rows[0]["dram_gb_s"] == pytest.approx(750.0)
 
 
 def test_profile_sweep_reduces_an_ncu_launch_list(tmp_path):
