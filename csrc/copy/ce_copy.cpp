@@ -121,6 +121,18 @@ int CeEngine::enqueue_once() {
   return (int)e;
 }
 
+// One copy of the list, enqueued by the CALLING thread with no synchronisation: the building
+// block of the "one runtime call per copy from the Python thread" comparator
+// (`Copy_Engine/nvlink_copy_engine_test.py:551-560` drives its copies that way).
+int CeEngine::enqueue_copy(int index) {
+  if (index < 0 || index >= (int)copies_.size()) return (int)cudaErrorInvalidValue;
+  const CeCopy& c = copies_[index];
+  return (int)cudaMemcpyPeerAsync(reinterpret_cast<void*>(c.dst), c.dst_dev,
+                                  reinterpret_cast<const void*>(c.src), c.src_dev, c.nbytes, stream_);
+}
+
+int CeEngine::synchronize() { return (int)cudaStreamSynchronize(stream_); }
+
 CeResult CeEngine::run_inline(int iters) {
   CeResult r;
   cudaSetDevice(device_);

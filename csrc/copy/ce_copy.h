@@ -48,6 +48,8 @@ class CeEngine {
 
   // Enqueue `iters` iterations and wait until the stream is drained. Blocking.
   CeResult run(int iters);
+  int enqueue_copy(int index);   // one peer memcpy from the calling thread, not synchronised
+  int synchronize();             // drain the engine's stream
   uint64_t stream_handle() const { return reinterpret_cast<uint64_t>(stream_); }
   int num_copies() const { return (int)copies_.size(); }
   uint64_t bytes_per_iter() const;

@@ -58,6 +58,17 @@ def time_engine(copies, mode: str, dev: int, iters: int, ctas_per_copy: int = 8)
     return r["wall_seconds"] / iters
 
 
+def time_engine_python(copies, dev: int, iters: int) -> float:
+    """One peer memcpy per runtime call from the Python thread (how the reference submits)."""
+    eng = K.CopyEngine(copies, "separate", stream_device=dev, use_proxy=False)
+    eng.run_from_python(2)
+    D.barrier()
+    secs = eng.run_from_python(iters)
+    D.barrier()
+    del eng
+    return secs / iters
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--min-bytes", dest="min", type=parse_nbytes, default=parse_nbytes("4K"))
@@ -132,6 +143,7 @@ def main() -> int:
                 ce = [(d_t.data_ptr(), w.peer_device(dst_rank), s_t.data_ptr(), w.device.index, n)]
                 variants = {
                     "ce": lambda: time_engine(ce, "separate", w.device.index, it),
+                    "ce_python": lambda: time_engine_python(ce, w.device.index, it),
                     "lsu16": lambda: time_kernel(lambda L: K.lsu_copy(d_t, s_t, n, ctas=c, threads=512, vec_bytes=16, launches=L), it),
                     "lsu32": lambda: time_kernel(lambda L: K.lsu_copy(d_t, s_t, n, ctas=c, threads=512, vec_bytes=32, launches=L), it),
                     "lsu16_overlap": lambda: time_kernel(lambda L: K.lsu_copy(
@@ -157,6 +169,7 @@ def main() -> int:
                             K.lsu_copy(v, s_t, n, ctas=c, threads=512, vec_bytes=vec)
                 variants = {
                     "ce": lambda: time_engine(ce, "separate", w.device.index, it),
+                    "ce_python": lambda: time_engine_python(ce, w.device.index, it),
                     "ce_graph": lambda: time_engine(ce, "graph", w.device.index, it),
                     "sm_batched": lambda: time_engine(ce, "kernel", w.device.index, it, ctas_per_copy=max(c, 1)),
                     "lsu16": lambda: time_kernel(lambda L: lsu_all(16, L), it),
@@ -189,6 +202,8 @@ def main() -> int:
                 secs = fn()
                 emit(pattern, n, name, secs, moved)
                 slow = records[-1]["seconds_slowest"]
+                if name == "ce_python":
+                    continue            # comparator column only, never a selectable variant
                 if best is None or slow < best[1]:
                     best = (name, slow)
             status.check()

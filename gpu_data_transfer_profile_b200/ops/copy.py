@@ -138,6 +138,24 @@ class CopyEngine:
             raise RuntimeError(f"{r['where']} failed: {r['error_string']} ({r['error']})")
         return r
 
+    def run_from_python(self, iters: int) -> float:
+        """The reference's submission path (`Copy_Engine/nvlink_copy_engine_test.py:551-560`): the
+        Python thread makes ONE runtime call per copy, `iters` times over the list, then drains the
+        stream once; returns wall seconds. The comparator that shows what the native loop and the
+        proxy thread of `run()` buy."""
+        import time
+        eng, n = self._eng, self._eng.num_copies
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            for i in range(n):
+                e = eng.enqueue_copy(i)
+                if e:
+                    raise RuntimeError(f"peer memcpy failed with CUDA error {e}")
+        e = eng.synchronize()
+        if e:
+            raise RuntimeError(f"stream synchronize failed with CUDA error {e}")
+        return time.perf_counter() - t0
+
     @property
     def bytes_per_iter(self) -> int:
         return self._eng.bytes_per_iter

@@ -24,6 +24,8 @@ virtual ranks living on ONE GPU (`LocalWorld`) can be driven phase by phase.
 """
 from __future__ import annotations
 
+import contextlib
+
 from dataclasses import dataclass, field
 from typing import List, Optional, Tuple
 
@@ -136,6 +138,7 @@ class _Carve:
         return out
 
 
+_NULL_CONTEXT = contextlib.nullcontext()
 _ELEM_DTYPE = {torch.bfloat16: "bfloat16", torch.float16: "float16", torch.float32: "float32"}
 _STATUS_MIRROR_SLOT = 4000     # int index inside the mapped host block that mirrors the status word
 
@@ -217,6 +220,7 @@ class Buffer:
             self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
             self.status.view(torch.int64)[1] = self.host_word + 4 * _STATUS_MIRROR_SLOT
             self.counters = torch.zeros(8, dtype=torch.int32, device=self.device)
+            self._ctr = [self.counters[i:i + 1] for i in range(8)]     # views made once, not per call
             self._side_stream = (torch.cuda.current_stream() if self.world.local
                                  else torch.cuda.Stream(device=self.device))
             self.comm_stream = None
@@ -333,6 +337,12 @@ class Buffer:
             self.comm_stream.wait_stream(compute)
         return compute
 
+    def _on_stream(self):
+        """Context for the launches of one op: the communication stream when the op is
+        asynchronous, nothing at all (no stream object, no device lookup) when it runs on the
+        caller's stream."""
+        return torch.cuda.stream(self.comm_stream) if self.comm_stream is not None else _NULL_CONTEXT
+
     def _exit(self, compute, async_finish, tensors) -> Optional[EventOverlap]:
         if compute is None:
             return EventOverlap(EventHandle()) if async_finish else None
@@ -349,7 +359,7 @@ class Buffer:
         """Device-side barrier over the group on the communication stream."""
         self._epoch["barrier"] += 1
         self._enter(None, False, False)
-        with torch.cuda.stream(self.comm_stream):
+        with self._on_stream():
             self.C.barrier(self.peers, 0, self.rank, self.group_size, self._epoch["barrier"],
                            self._timeout_ns(), self.status_ptr, not self.world.local)
 
@@ -359,7 +369,7 @@ class Buffer:
         `clear=False` the fault is left recorded, as after a real time-out: the next public op on
         this buffer raises it."""
         self._enter(None, False, False)
-        with torch.cuda.stream(self.comm_stream):
+        with self._on_stream():
             self.C.wait_flags(self.region.local_ptr, 0, self.C.NUM_CHANNELS - 1, 1, 1 << 30,
                               int(timeout_s * 1e9), self.status_ptr, 8)
         code = int(self.status[0].item())
@@ -381,7 +391,7 @@ class Buffer:
             topk_idx = topk_idx.to(torch.int64)
         topk_idx = topk_idx.contiguous()
         compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
-        with torch.cuda.stream(self.comm_stream):
+        with self._on_stream():
             T = topk_idx.shape[0]
             need = self.C.layout_scratch_ints(T, num_experts, R)
             if self._layout_ws is None or self._layout_ws.numel() < need:
@@ -390,7 +400,7 @@ class Buffer:
             per_rank, per_expert = counts[:R], counts[R:]
             in_rank = torch.empty((T, R), dtype=torch.bool, device=self.device)
             self.C.layout(topk_idx, num_experts, R, per_rank, per_expert, in_rank, self._layout_ws,
-                          self.counters[4:5], self.status_ptr)
+                          self._ctr[4], self.status_ptr)
         ev = self._exit(compute, async_finish, (per_rank, per_expert, in_rank, topk_idx))
         return per_rank, None, per_expert, in_rank, ev
 
@@ -487,7 +497,7 @@ class Buffer:
                            st.get("is_token_in_rank") if mode == 0 else None,
                            st["topk_idx"] if mode == 1 else None,
                            per_expert if mode == 0 else None,
-                           st["item_rank"], st["chunk_hist"], self.counters[0:1], self.status_ptr)
+                           st["item_rank"], st["chunk_hist"], self._ctr[0], self.status_ptr)
         return st
 
     def _dispatch_p2(self, st):
@@ -507,7 +517,7 @@ class Buffer:
         self.C.dispatch_send(geom, regions, self.peers, st["meta"], st["x"], st["fp8"], st["cached"],
                              st["topk_idx"], st.get("topk_weights"), st.get("item_rank"),
                              st.get("chunk_hist"), st["send_row"], st["send_slot"],
-                             self.counters[1:2], self.host_word, self.status_ptr, self._blocks(),
+                             self._ctr[1], self.host_word, self.status_ptr, self._blocks(),
                              st.get("scales_in"))
 
     def _dispatch_p3(self, st, zero_copy: bool, num_worst_tokens: int = 0, expert_alignment: int = 1):
@@ -589,7 +599,7 @@ class Buffer:
         if expert_alignment < 1:
             raise ValueError("expert_alignment must be >= 1")
         compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
-        with torch.cuda.stream(self.comm_stream):
+        with self._on_stream():
             st = self._dispatch_p1(x, handle, is_token_in_rank, num_tokens_per_expert, topk_idx,
                                    topk_weights, use_fp8, group_by_expert, num_experts)
             self._dispatch_p2(st)
@@ -634,7 +644,7 @@ class Buffer:
         """Push form, send half as its own launch (several virtual ranks on one GPU)."""
         st = self._combine_prepare(x, handle, topk_weights)
         self.C.combine(st["geom"], st["regions"], self.peers, 1, max(1, Buffer.num_sms), False,
-                       handle.n_recv_dev, handle.recv_meta, x, st["topk_w"], self.counters[2:3],
+                       handle.n_recv_dev, handle.recv_meta, x, st["topk_w"], self._ctr[2],
                        None, None, None, None, self.status_ptr)
         return st
 
@@ -642,7 +652,7 @@ class Buffer:
         """Push form, reduce half as its own launch (waits for every rank's combine flag first)."""
         out, out_w = self._combine_outputs(st, handle)
         self.C.combine(st["geom"], st["regions"], self.peers, 2, max(1, Buffer.num_sms), True,
-                       None, None, None, None, self.counters[2:3],
+                       None, None, None, None, self._ctr[2],
                        handle.send_slot, weights, out, out_w, self.status_ptr)
         return out, out_w
 
@@ -652,7 +662,7 @@ class Buffer:
         st = self._combine_prepare(x, handle, topk_weights)
         out, out_w = self._combine_outputs(st, handle)
         self.C.combine(st["geom"], st["regions"], self.peers, 0, max(1, Buffer.num_sms), True,
-                       handle.n_recv_dev, handle.recv_meta, x, st["topk_w"], self.counters[2:3],
+                       handle.n_recv_dev, handle.recv_meta, x, st["topk_w"], self._ctr[2],
                        handle.send_slot, weights, out, out_w, self.status_ptr)
         return out, out_w
 
@@ -730,7 +740,7 @@ class Buffer:
         compute = self._enter(previous_event, allocate_on_comm_stream, async_finish)
         if topk_weights is not None and topk_weights.dtype != torch.float32:
             topk_weights = topk_weights.to(torch.float32)
-        with torch.cuda.stream(self.comm_stream):
+        with self._on_stream():
             if self._use_pull(x, topk_weights):
                 if self._single_launch:
                     out, out_w = self._combine_pull(0, x, handle, topk_weights, item_weights)
@@ -856,13 +866,13 @@ class Buffer:
         synchronisation; may be captured in a CUDA graph. With return_recv_hook=True only the send half is launched and
         the returned hook launches the receive half (then fills the same tensors)."""
         compute = self._enter(None, False, False)
-        with torch.cuda.stream(self.comm_stream):
+        with self._on_stream():
             d = self._ll_dispatch_send(x, topk_idx, num_max_dispatch_tokens_per_rank, num_experts, use_fp8)
             if return_recv_hook:
                 box = {}
 
                 def hook():
-                    with torch.cuda.stream(self.comm_stream):
+                    with self._on_stream():
                         box["out"] = self._ll_dispatch_recv(d)
                     return box["out"]
                 ev = self._exit(compute, async_finish, [x])
@@ -935,17 +945,17 @@ class Buffer:
         of the group must use the same form."""
         compute = self._enter(None, False, False)
         if zero_copy or self._ll_is_combine_buffer(x, handle):
-            with torch.cuda.stream(self.comm_stream):
+            with self._on_stream():
                 res = self._ll_combine_pull(0 if self._single_launch else 1, topk_idx, topk_weights, handle, out)
                 if not self._single_launch:
                     res = self._ll_combine_pull(2, topk_idx, topk_weights, handle, res)
             ev = self._exit(compute, async_finish, [res])
             return res, ev, ((lambda: res) if return_recv_hook else None)
-        with torch.cuda.stream(self.comm_stream):
+        with self._on_stream():
             c = self._ll_combine_send(x, handle)
             if return_recv_hook:
                 def hook():
-                    with torch.cuda.stream(self.comm_stream):
+                    with self._on_stream():
                         return self._ll_combine_recv(c, topk_idx, topk_weights, out)
                 return None, self._exit(compute, async_finish, [x]), hook
             res = self._ll_combine_recv(c, topk_idx, topk_weights, out)
@@ -1014,7 +1024,7 @@ def _fused_fc2_send(self: Buffer, act: torch.Tensor, w2: torch.Tensor, handle: D
     expert_off = handle.meta[2 + El: 2 + El + El + 1]
     flag_row = self.C.MAX_RANKS * 4 * 2          # byte offset of the combine channel's flag row
     G.grouped_gemm_combine(act, w2, expert_off, handle.recv_meta, self.peers, regions[8], carve.slot_cap,
-                           self.rank, signal_flag_off=flag_row, epoch=ep, counter=self.counters[3:4],
+                           self.rank, signal_flag_off=flag_row, epoch=ep, counter=self._ctr[3],
                            status_ptr=self.status_ptr)
     geom = self._geom(E=handle.E, K=handle.K, T=handle.T, mode=1, H=handle.H, cap=handle.n_recv,
                       slot_cap=carve.slot_cap, epoch=ep)
@@ -1027,7 +1037,7 @@ def _fused_fc2_combine(self: Buffer, act: torch.Tensor, w2: torch.Tensor, handle
     tokens. act: bf16 [N_recv, F] rows grouped by local expert (expert-mode handle), w2: bf16
     [E_local, H, F]. Returns combined [T, H] bf16."""
     compute = self._enter(None, False, False)
-    with torch.cuda.stream(self.comm_stream):
+    with self._on_stream():
         st = _fused_fc2_send(self, act, w2, handle)
         out, _ = self._combine_p2(st, handle, item_weights)
     self._exit(compute, False, [out, act])

@@ -102,6 +102,26 @@ def test_copy_engine_modes(mode, proxy):
         o += s + 64
 
 
+def test_copy_engine_python_thread_comparator():
+    """One runtime call per copy from the Python thread (the reference's submission path):
+    same bytes land, gaps stay untouched, a bad index is an error code and not a crash."""
+    from gpu_data_transfer_profile_b200.ops.copy import CopyEngine
+    sizes = [4096, 100000, 16]
+    src = _pattern(sum(sizes) + 3 * 64, 9)
+    dst = torch.full((sum(sizes) + 3 * 64,), 253, dtype=torch.uint8, device="cuda")
+    copies, o = [], 0
+    for s in sizes:
+        copies.append((dst.data_ptr() + o, 0, src.data_ptr() + o, 0, s))
+        o += s + 64
+    eng = CopyEngine(copies, "separate", stream_device=0, use_proxy=False)
+    assert eng.run_from_python(3) > 0
+    o = 0
+    for s in sizes:
+        assert torch.equal(dst[o:o + s], src[o:o + s]) and bool((dst[o + s:o + s + 64] == 253).all())
+        o += s + 64
+    assert eng._eng.enqueue_copy(len(sizes)) != 0 and eng._eng.enqueue_copy(-1) != 0
+
+
 @pytest.mark.parametrize("mod,extra", [
     ("copy_engine", ["--nbytes", "1M", "--copies-per-iter", "4", "--copy-mode", "batch"]),
     ("copy_engine", ["--nbytes", "256K", "--copies-per-iter", "3", "--non-uniform-copy-size", "--mode", "reverse-ring"]),
