@@ -7,8 +7,10 @@
 Parity: the seven plotters under `Copy_Engine/Results/*/plot_*.py` and
 `LSU_TMA/Results/plot_nvlink_lsu_tma_sm_summary.py` (discover `.sqlite` files by name, call the
 sibling analyzer, print the values table, write throughput / gap+duration / NVLink RX-TX
-figures). The table (stdout + CSV + JSON) is always produced; PNG files need matplotlib (Agg
-backend, CPU rasterisation) and are skipped with a note when it is not installed.
+figures). The table (stdout + CSV + JSON) is always produced. Figures are PNG files when
+matplotlib is installed (Agg backend, CPU rasterisation); without it the same line plots are
+written as SVG files by a small built-in renderer, so a machine with nothing but Python still
+gets its figures.
 """
 from __future__ import annotations
 
@@ -60,10 +62,91 @@ def _have_matplotlib():
         return False
 
 
+_COLOURS = ("#1f77b4", "#ff7f0e", "#2ca02c", "#d62728", "#9467bd", "#8c564b", "#e377c2", "#7f7f7f", "#bcbd22", "#17becf")
+
+
+def _curves(rows, x, ys, series):
+    """[(label, [(x, y), ...])] in the order both renderers draw them."""
+    out = []
+    keys = sorted({r.get(series) for r in rows}, key=str) if series else [None]
+    for k in keys:
+        sel = sorted((r for r in rows if (not series or r.get(series) == k) and r.get(x) is not None), key=lambda r: r[x])
+        for y in ys:
+            pts = [(float(r[x]), float(r[y])) for r in sel if r.get(y) is not None]
+            if pts:
+                label = " ".join(str(v) for v in (k, y if len(ys) > 1 else None) if v is not None) or y
+                out.append((label, pts))
+    return out
+
+
+def _fmt_tick(v: float, is_bytes: bool) -> str:
+    if is_bytes:
+        for unit, sz in (("G", 1 << 30), ("M", 1 << 20), ("K", 1 << 10)):
+            if v >= sz:
+                return f"{v / sz:g}{unit}"
+    return f"{v:g}"
+
+
+def svg_line_plot(rows: List[Dict[str, Any]], x: str, ys: Sequence[str], series: Optional[str], title: str,
+                  ylabel: str, path: Path, logx: bool = True) -> bool:
+    """Dependency-free renderer: one polyline with markers and value labels per curve, log2 or
+    linear x axis, linear y axis from 0, legend on the right. Returns False when nothing is
+    plottable."""
+    import math
+    from xml.sax.saxutils import escape
+    curves = _curves(rows, x, ys, series)
+    if not curves:
+        return False
+    xs = [p[0] for _, pts in curves for p in pts]
+    ymax = max(p[1] for _, pts in curves for p in pts) or 1.0
+    use_log = logx and min(xs) > 0
+    fx = (lambda v: math.log2(v)) if use_log else (lambda v: v)
+    x0, x1 = fx(min(xs)), fx(max(xs))
+    if x1 == x0:
+        x0, x1 = x0 - 1, x1 + 1
+    W, H, L, R, T, B = 960, 540, 70, 220, 40, 60
+    px = lambda v: L + (fx(v) - x0) / (x1 - x0) * (W - L - R)
+    py = lambda v: H - B - v / (ymax * 1.08) * (H - T - B)
+    el = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{W}" height="{H}" font-family="sans-serif" font-size="11">',
+          f'<rect width="{W}" height="{H}" fill="white"/>',
+          f'<text x="{(L + W - R) / 2}" y="22" text-anchor="middle" font-size="15">{escape(title)}</text>',
+          f'<text x="{(L + W - R) / 2}" y="{H - 14}" text-anchor="middle">{escape(x)}</text>',
+          f'<text transform="translate(16,{(T + H - B) / 2}) rotate(-90)" text-anchor="middle">{escape(ylabel)}</text>']
+    step = 10 ** math.floor(math.log10(ymax * 1.08 / 4)) if ymax > 0 else 1.0
+    step = next(m * step for m in (1, 2, 5, 10) if ymax * 1.08 / (m * step) <= 8)
+    v = 0.0
+    while v <= ymax * 1.08:
+        el.append(f'<line x1="{L}" y1="{py(v):.1f}" x2="{W - R}" y2="{py(v):.1f}" stroke="#ddd"/>')
+        el.append(f'<text x="{L - 6}" y="{py(v) + 4:.1f}" text-anchor="end">{v:g}</text>')
+        v += step
+    ticks = sorted(set(xs))
+    if len(ticks) > 14:
+        ticks = ticks[::math.ceil(len(ticks) / 14)]
+    for t in ticks:
+        el.append(f'<line x1="{px(t):.1f}" y1="{H - B}" x2="{px(t):.1f}" y2="{H - B + 5}" stroke="black"/>')
+        el.append(f'<text x="{px(t):.1f}" y="{H - B + 18}" text-anchor="middle">{_fmt_tick(t, x in ("nbytes", "bytes"))}</text>')
+    el.append(f'<rect x="{L}" y="{T}" width="{W - L - R}" height="{H - T - B}" fill="none" stroke="black"/>')
+    for i, (label, pts) in enumerate(curves):
+        c = _COLOURS[i % len(_COLOURS)]
+        el.append(f'<polyline fill="none" stroke="{c}" stroke-width="1.6" points="' +
+                  " ".join(f"{px(a):.1f},{py(b):.1f}" for a, b in pts) + '"/>')
+        for a, b in pts:
+            el.append(f'<circle cx="{px(a):.1f}" cy="{py(b):.1f}" r="2.6" fill="{c}"/>')
+            el.append(f'<text x="{px(a):.1f}" y="{py(b) - 6:.1f}" text-anchor="middle" font-size="8">{b:.3g}</text>')
+        ly = T + 14 + 16 * i
+        el.append(f'<line x1="{W - R + 12}" y1="{ly - 4}" x2="{W - R + 36}" y2="{ly - 4}" stroke="{c}" stroke-width="2"/>')
+        el.append(f'<text x="{W - R + 42}" y="{ly}">{escape(label)}</text>')
+    el.append("</svg>")
+    path.parent.mkdir(parents=True, exist_ok=True)
+    path.write_text("\n".join(el))
+    return True
+
+
 def line_plot(rows: List[Dict[str, Any]], x: str, ys: Sequence[str], series: Optional[str], title: str,
               ylabel: str, path: Path, logx: bool = True) -> bool:
+    """PNG through matplotlib when it is installed, else the same figure as `<path>.svg`."""
     if not _have_matplotlib():
-        return False
+        return svg_line_plot(rows, x, ys, series, title, ylabel, path.with_suffix(".svg"), logx)
     import matplotlib.pyplot as plt
     fig, ax = plt.subplots(figsize=(8, 4.5))
     keys = sorted({r.get(series) for r in rows}, key=str) if series else [None]
@@ -164,7 +247,7 @@ def main(argv=None) -> int:
         write_table(rows, out, a.path.stem + "_table")
         ok = line_plot(rows, a.x, [a.y], a.series, a.path.stem, a.y, out / f"{a.path.stem}_{a.y}.png",
                        logx=a.x in ("nbytes", "bytes"))
-        print(f"[plot] {'written' if ok else 'skipped (matplotlib not installed)'}")
+        print(f"[plot] {'figure written' if ok else 'no plottable rows'}" + ("" if _have_matplotlib() else " (SVG: matplotlib not installed)"))
         return 0
     builder, x, series, title = KINDS[a.kind]
     rows = collect(a.path, builder, bus_id=a.gpu_bus_id, peak_gb_s=a.nvlink_peak_gb_s)
@@ -181,7 +264,7 @@ def main(argv=None) -> int:
         line_plot(rows, x, ["nvlink_rx", "nvlink_tx"], series, f"{title}: NVLink RX/TX", "% of peak",
                   out / f"{a.kind}_nvlink.png", logx),
     ]
-    print(f"[plot] {sum(made)} figure(s) written" + ("" if all(made) else " (matplotlib not installed: tables only)"))
+    print(f"[plot] {sum(made)} figure(s) written" + ("" if _have_matplotlib() else " as SVG (matplotlib not installed)"))
     return 0
 
 

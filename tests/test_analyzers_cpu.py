@@ -120,6 +120,23 @@ def test_kernel_summary_and_outputs(tmp_path, capsys):
     assert P.main(["sm", str(tmp_path), "--out", str(tmp_path / "o")]) == 0
     rows = json.loads((tmp_path / "o" / "sm_summary.json").read_text())
     assert rows and rows[0]["sms"] == 4 and rows[0]["method"] == "lsu"
+    # figures are always produced: PNG with matplotlib, else SVG from the built-in renderer
+    figs = list((tmp_path / "o").glob("sm_timing.*"))
+    assert figs and figs[0].suffix in (".png", ".svg") and figs[0].stat().st_size > 500
+
+
+def test_svg_renderer_draws_one_polyline_per_curve(tmp_path):
+    import xml.dom.minidom as minidom
+    rows = [dict(nbytes=1 << (10 + i), gbs=10.0 * (i + 1) * (2 if v == "b" else 1), variant=v) for i in range(5) for v in "ab"]
+    out = tmp_path / "f.svg"
+    assert P.svg_line_plot(rows, "nbytes", ["gbs"], "variant", "t <&>", "GB/s", out)
+    doc = minidom.parse(str(out))
+    lines = doc.getElementsByTagName("polyline")
+    assert len(lines) == 2 and all(len(l.getAttribute("points").split()) == 5 for l in lines)
+    # the highest value sits above the lowest one (y grows downwards in SVG)
+    ys = [float(p.split(",")[1]) for p in lines[1].getAttribute("points").split()]
+    assert ys[-1] < ys[0]
+    assert not P.svg_line_plot([], "nbytes", ["gbs"], None, "t", "y", tmp_path / "e.svg")
 
 
 def test_report_name_parsing_and_sqlite_resolution(tmp_path):
