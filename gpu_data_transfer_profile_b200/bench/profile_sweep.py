@@ -45,12 +45,12 @@ def summarize_launch_list(path: str) -> dict:
     return out
 
 
-def commands(gpus: int, out: str, iters: int, warmup: int):
+def commands(gpus: int, out: str, iters: int, warmup: int, batch_impl: str = "graph"):
     tr = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={gpus}",
           "--master-addr", "127.0.0.1", "--master-port", "29577"]
     pk = "gpu_data_transfer_profile_b200.bench."
     common = ["--iters", str(iters), "--warmup", str(warmup), "--check"]
-    for mib in range(1, 11):
+    for mib in range(1, 11 if gpus >= 2 else 0):           # the fan-out needs a peer: skipped on one GPU
         for mode in ("separate", "batch"):
             yield (f"a2a_{mode}_{mib}M", tr + ["-m", pk + "a2a_copy", "--nbytes", f"{mib}M", "--copy-mode", mode,
                                                 "--jsonl", os.path.join(out, "a2a.jsonl")] + common)
@@ -59,7 +59,8 @@ def commands(gpus: int, out: str, iters: int, warmup: int):
             for mode in ("separate", "batch"):
                 yield (f"layout_{layout}_{mode}_4x{kib}K",
                        tr + ["-m", pk + "layout_copy", "--nbytes", f"{kib}K", "--copies-per-iter", "4", "--layout", layout,
-                             "--copy-mode", mode, "--jsonl", os.path.join(out, "layout.jsonl")] + common)
+                             "--copy-mode", mode, "--batch-impl", batch_impl,
+                             "--jsonl", os.path.join(out, "layout.jsonl")] + common)
 
 
 def main() -> int:
@@ -84,7 +85,9 @@ def main() -> int:
         print("--tool ncu needs the ncu CLI and --gpus 1 (a multi-rank command is never put under ncu)", file=sys.stderr)
         return 2
     rc = 0
-    for name, cmd in commands(a.gpus, a.out, a.iters, a.warmup):
+    # under ncu only kernels are listed: a batch is then submitted as ONE SM-kernel launch over a
+    # descriptor table instead of a graph of memcpy nodes, so the launch list shows the batch
+    for name, cmd in commands(a.gpus, a.out, a.iters, a.warmup, "kernel" if ncu else "graph"):
         if a.only and a.only not in name:
             continue
         if ncu:
