@@ -80,12 +80,15 @@ def main() -> int:
 
     # The step combines the zero-copy receive rows in place (pull form), so the buffer needs no
     # combine slots: that halves the symmetric region (worst-case receive rows x 2 epoch parities).
-    cfg = Buffer.get_dispatch_config(world, T, K, E, combine_slots=False)
+    # With --fp8 the rows to combine are the experts' bf16 output, a tensor of its own outside the
+    # region: that run keeps the slots and combines in the push form.
+    slots = bool(args.fp8)
+    cfg = Buffer.get_dispatch_config(world, T, K, E, combine_slots=slots)
     nbytes = cfg.get_nvl_buffer_size_hint(H * 2, world)
     if world > 1:
-        buf = Buffer(torch.distributed.group.WORLD, nbytes, 0, combine_slots=False)
+        buf = Buffer(torch.distributed.group.WORLD, nbytes, 0, combine_slots=slots)
     else:
-        buf = Buffer(None, nbytes, 0, world=LocalWorld.make(1, dev)[0], combine_slots=False)
+        buf = Buffer(None, nbytes, 0, world=LocalWorld.make(1, dev)[0], combine_slots=slots)
 
     # ---- seeded synthetic inputs, staged in pinned host memory for the end-to-end arm ----
     g = torch.Generator().manual_seed(1234 + rank)
@@ -227,7 +230,9 @@ def main() -> int:
             "config": {"model": MODEL, "global_batch": int(total_tokens), "seq_len": T,
                        "parallelism": f"ep{world}", "hidden": H, "experts": E, "topk": K,
                        "zipf_s": args.zipf, "l2": "flushed between steps (252 MiB write)",
-                       "combine": "pull form: rows are read from the peers' receive regions and reduced in one pass",
+                       "combine": ("push form: the experts' bf16 output is stored into slots on the source ranks, then reduced"
+                                   if args.fp8 else
+                                   "pull form: rows are read from the peers' receive regions and reduced in one pass"),
                        "receive": "zero-copy views of the symmetric receive region, "
                                   + ("sized by a host read of the count" if args.host_count else "num_worst_tokens = world x tokens (no host sync)"),
                        "num_sms_knob": Buffer.num_sms,
@@ -244,7 +249,8 @@ def main() -> int:
                     "d2h_bytes_per_step": 4,
                     "pipelining": "inputs double-buffered: the H2D copy of step i+1 overlaps step i"},
             "gpu_launches": 4 * args.steps,
-            "launches_per_step": "layout_kernel, notify_send_kernel, dispatch_send_kernel, combine_pull_kernel",
+            "launches_per_step": ("layout_cluster_kernel, notify_send_cluster_kernel, dispatch_send_kernel, " +
+                                  ("combine_kernel" if args.fp8 else "combine_pull_kernel")),
             "symmetric_bytes_reserved_per_rank": buf.bytes_reserved,
             "check": "ok" if ok else f"FAIL max_err={err:.4f}",
             "impl": "ours",
