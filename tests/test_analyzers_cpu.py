@@ -187,3 +187,18 @@ def test_profile_sweep_dry_run_with_ncu_tool_refuses_multi_rank(capsys):
         assert P.main() == 2
     finally:
         sys.argv = argv
+
+
+def test_profile_sweep_command_lists():
+    """Eight GPUs: the reference's two sweeps (fan-out 1-10 MiB x 2 modes, 9 sizes x 4 layouts x 2
+    modes). One GPU: no fan-out runs (they need a peer); under ncu a batch is one SM-kernel launch."""
+    from gpu_data_transfer_profile_b200.bench.profile_sweep import commands
+    full = list(commands(8, "out", 100, 10))
+    assert len(full) == 10 * 2 + 9 * 4 * 2
+    assert sum(n.startswith("a2a_") for n, _ in full) == 20 and "--nproc-per-node=8" in full[0][1]
+    one = list(commands(1, "out", 5, 2, "kernel"))
+    assert len(one) == 72 and all(n.startswith("layout_") for n, _ in one)
+    name, cmd = one[1]
+    assert name == "layout_contiguous_batch_4x8K"
+    assert cmd[cmd.index("--batch-impl") + 1] == "kernel" and cmd[cmd.index("--copy-mode") + 1] == "batch"
+    assert cmd[cmd.index("--iters") + 1] == "5" and "--check" in cmd
