@@ -108,19 +108,24 @@ class _Carve:
                      comb_x=comb_row_bytes if combine_slots else 0, comb_w=K * 4 if combine_slots else 0)
         self.combine_slots = bool(combine_slots)
         per_row = sum(sizes.values())
-        avail = nbytes - FIXED_BYTES - 2 * len(sizes) * REGION_ALIGN
+        avail = nbytes - FIXED_BYTES - 2 * len(sizes) * (REGION_ALIGN + GUARD_BYTES)
         self.cap = max(avail // (2 * per_row), 0)
         if max_recv_rows > 0:
             self.cap = min(self.cap, int(max_recv_rows))
         # without slots the slot numbers that dispatch computes are never used as addresses
         self.slot_cap = self.cap if combine_slots else (1 << 30)
         self.regions = []  # per parity: dict name -> offset
+        # Every region is followed by a guard band of at least GUARD_BYTES that no kernel may
+        # write: (region name, parity, first byte, length). `Buffer.check_canaries` verifies them.
+        self.guards = []
         off = FIXED_BYTES
-        for _ in range(2):
+        for parity in range(2):
             d = {}
             for name, sz in sizes.items():
                 d[name] = off
-                off = align_up(off + self.cap * sz, REGION_ALIGN)
+                end = off + self.cap * sz
+                off = align_up(end + GUARD_BYTES, REGION_ALIGN)
+                self.guards.append((name, parity, end, off - end))
             self.regions.append(d)
         assert off <= nbytes or self.cap == 0
         self.bytes_used = off
@@ -138,6 +143,8 @@ class _Carve:
         return out
 
 
+GUARD_BYTES = 256              # canary band after every receive / combine region
+CANARY = 0xA5
 _NULL_CONTEXT = contextlib.nullcontext()
 _ELEM_DTYPE = {torch.bfloat16: "bfloat16", torch.float16: "float16", torch.float32: "float32"}
 _STATUS_MIRROR_SLOT = 4000     # int index inside the mapped host block that mirrors the status word
@@ -299,7 +306,26 @@ class Buffer:
             self._ll = None
             self._carve = _Carve(self.num_nvl_bytes, self.group_size, E, K, H, row_bytes, comb_row_bytes,
                                  self.num_max_recv_tokens, self.combine_slots)
+            # paint the guard bands of MY region; peers store into it only after they have seen
+            # this rank's next count vector, which is stream-ordered after these fills
+            for _, _, off, n in self._carve.guards:
+                self.region.view(off, (n,), "uint8").fill_(CANARY)
         return self._carve
+
+    def check_canaries(self) -> None:
+        """Synchronising debug check: every guard band behind a receive / combine region of this
+        rank still holds its fill pattern. A kernel (this rank's or a peer's) that stored past
+        the end of a region would have hit one first. Raises `EpStatusError` naming the region."""
+        carve = self._carve
+        if carve is None:
+            return
+        bad = []
+        for name, parity, off, n in carve.guards:
+            v = self.region.view(off, (n,), "uint8")
+            if bool((v != CANARY).any()):
+                bad.append(f"{name}[parity {parity}] at byte {off}")
+        if bad:
+            raise EpStatusError("guard band overwritten behind " + ", ".join(bad))
 
     def _geom(self, *, E, K, T, mode, H, cap, slot_cap, epoch, epoch_wait=0, tail_wait=0) -> List[int]:
         R = self.group_size

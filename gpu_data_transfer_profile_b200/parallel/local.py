@@ -81,6 +81,10 @@ class LocalGroup:
         for b in self.buffers:
             b.check_status()
 
+    def check_canaries(self):
+        for b in self.buffers:
+            b.check_canaries()
+
     def destroy(self):
         for b in self.buffers:
             b.destroy()

@@ -79,6 +79,7 @@ def test_dispatch_combine_rank_mode(R, T, H, E, K, dtype):
             torch.testing.assert_close(got.cpu().float(), cref[s], atol=tol * 8, rtol=tol)
             torch.testing.assert_close(got_w.cpu(), wref[s], atol=1e-6, rtol=1e-6)
         g.check_status()
+        g.check_canaries()
     finally:
         g.destroy()
 
@@ -105,6 +106,7 @@ def test_dispatch_combine_expert_mode(R, T, H, E, K):
         for s in range(R):
             torch.testing.assert_close(comb[s][0].cpu().float(), xs[s].float(), atol=3e-2, rtol=2e-2)
         g.check_status()
+        g.check_canaries()
     finally:
         g.destroy()
 
@@ -219,6 +221,38 @@ def test_receive_bound_overflow_is_a_status_not_a_fault():
                                          num_tokens_per_expert=pe)
         assert torch.equal(rx, x2)
         buf.check_status()
+        buf.check_canaries()        # the skipped rows of the overflowing call touched no guard band
+    finally:
+        buf.destroy()
+
+
+def test_guard_bands_are_checked_and_a_stray_store_is_named():
+    """Every region of the carve ends in a painted guard band; `check_canaries` passes after real
+    traffic (receive region filled to its last row) and names the region behind which a byte changed."""
+    from gpu_data_transfer_profile_b200.parallel.buffer import CANARY, Buffer, EpStatusError
+    from gpu_data_transfer_profile_b200.parallel.symm import LocalWorld
+    T, H, E, K = 64, 256, 8, 2
+    buf = Buffer(None, 32 << 20, world=LocalWorld.make(1)[0], timeout_s=2.0, num_max_recv_tokens=T)
+    try:
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        idx, w = O.make_routing(T, E, K, 5)
+        idx, w = idx.cuda(), w.cuda()
+        for _ in range(3):          # both epoch parities; T rows = exactly the capacity
+            pr, _, pe, inr, _ = buf.get_dispatch_layout(idx, E)
+            rx, _, _, _, h, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, is_token_in_rank=inr,
+                                             num_tokens_per_expert=pe)
+            out, _, _ = buf.combine(rx, h)
+            assert rx.shape[0] == T == buf._carve.cap
+        buf.check_status()
+        buf.check_canaries()
+        name, parity, off, n = buf._carve.guards[0]
+        band = buf.region.view(off, (n,), "uint8")
+        assert bool((band == CANARY).all())
+        band[7] = 0                 # what a store one row past the region would do
+        with pytest.raises(EpStatusError, match=name):
+            buf.check_canaries()
+        band[7] = CANARY
+        buf.check_canaries()
     finally:
         buf.destroy()
 
@@ -279,6 +313,7 @@ def test_pull_combine_expert_mode_with_item_weights():
         for s in range(R):
             torch.testing.assert_close(comb[s][0].cpu().float(), xs[s].float(), atol=3e-2, rtol=2e-2)
         g.check_status()
+        g.check_canaries()
     finally:
         g.destroy()
 

@@ -211,3 +211,27 @@ def test_control_area_blocks_have_shape_independent_positions():
     assert (a.flags, a.pull_info) == (b.flags, b.pull_info)
     assert a.pull_info < a.counts[0] and a.counts[1] < a.ll_ctrl
     assert _Carve(64 << 20, 8, 256, 8, 1024, 2048, 2048, max_recv_rows=100).cap == 100
+
+
+def test_guard_bands_separate_every_region_and_fit_the_size_hint():
+    """Each receive / combine region ends in a guard band of >= 256 bytes that starts exactly at
+    the region's last byte + 1, touches nothing else, and the whole layout fits the size hint."""
+    from gpu_data_transfer_profile_b200.parallel.buffer import GUARD_BYTES, _Carve
+    from gpu_data_transfer_profile_b200.parallel.config import FIXED_BYTES, Config
+    for slots, bound in ((True, 0), (False, 0), (False, 3000)):
+        cfg = Config(24, num_max_tokens_per_rank=512, num_topk=8, num_experts=64,
+                     num_max_recv_tokens=bound, combine_slots=slots)
+        nbytes = cfg.get_nvl_buffer_size_hint(2048 * 2, 8)
+        c = _Carve(nbytes, 8, 64, 8, 2048, 4096, 4096, max_recv_rows=bound, combine_slots=slots)
+        assert c.cap >= (bound or 8 * 512) and c.bytes_used <= nbytes
+        spans = []
+        for par, d in enumerate(c.regions):
+            for name, off in d.items():
+                spans.append((off, name, par))
+        spans.sort()
+        assert len(c.guards) == len(spans) == 16 and spans[0][0] == FIXED_BYTES
+        guards = {(name, par): (g0, n) for name, par, g0, n in c.guards}
+        for i, (off, name, par) in enumerate(spans):
+            g0, n = guards[(name, par)]
+            nxt = spans[i + 1][0] if i + 1 < len(spans) else c.bytes_used
+            assert off <= g0 and n >= GUARD_BYTES and g0 + n == nxt     # band = [end of region, next region)
