@@ -7,6 +7,13 @@ duration, API-end -> copy-start wait, and NVLink RX/TX user-data percent of peak
 the copy/kernel window. Tables read: TARGET_INFO_GPU, ENUM_CUDA_MEMCPY_OPER,
 CUPTI_ACTIVITY_KIND_MEMCPY, CUPTI_ACTIVITY_KIND_RUNTIME, CUPTI_ACTIVITY_KIND_KERNEL, StringIds,
 PROCESSES, GPU_METRICS, TARGET_INFO_GPU_METRICS.
+
+Parity, by function of `Copy_Engine/Results/nvlink_copy_engine_test/analyze_nvlink_copy_engine_report.py`:
+report -> SQLite through `nsys export` (`:107-141`), peer-copy kind and GPU by PCI bus id
+(`:156-189`), source copy events joined to their runtime calls (`:191-254`), gap / wait / duration
+statistics (`:263-308`), NVLink RX/TX metrics averaged over the copy window (`:310-368`); kernel
+events by name for the SM copies as `LSU_TMA/Results/analyze_nvlink_lsu_tma_report.py:216-305`
+(name detection, launches with their durations) and `:328-389` (NVLink metrics over the kernel window).
 """
 from __future__ import annotations
 

@@ -7,7 +7,10 @@
 Parity: the seven plotters under `Copy_Engine/Results/*/plot_*.py` and
 `LSU_TMA/Results/plot_nvlink_lsu_tma_sm_summary.py` (discover `.sqlite` files by name, call the
 sibling analyzer, print the values table, write throughput / gap+duration / NVLink RX-TX
-figures). The table (stdout + CSV + JSON) is always produced. Figures are PNG files when
+figures): size from the file name and report discovery as
+`Copy_Engine/Results/nvlink_copy_engine_test/plot_nvlink_copy_engine_summary.py:90-128`, the three
+figure kinds as `:130-273`, SM-count / method classification of the SM-copy reports as
+`LSU_TMA/Results/plot_nvlink_lsu_tma_sm_summary.py:132-207` and its values table `:284-297`. The table (stdout + CSV + JSON) is always produced. Figures are PNG files when
 matplotlib is installed (Agg backend, CPU rasterisation); without it the same line plots are
 written as SVG files by a small built-in renderer, so a machine with nothing but Python still
 gets its figures.

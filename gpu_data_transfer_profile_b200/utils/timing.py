@@ -1,5 +1,11 @@
 """Device-side timing: CUDA events on the launching stream, L2 flush between iterations,
-max over ranks. Never wall clock for kernels."""
+max over ranks. Never wall clock for kernels.
+
+The reference times its EP steps the same way, one CUDA-event pair per iteration
+(`DeepEP_v1/deepep_v1_dispatch.py:186-248`), and its copy-engine loops by wall clock around the
+enqueue loop plus one stream synchronise (`Copy_Engine/nvlink_copy_engine_test.py:548-560`; that
+form lives in `csrc/copy/ce_copy.cpp`, where the copies are not kernels). Added here: the L2 flush
+between iterations and the reduction to the slowest rank."""
 from __future__ import annotations
 
 from typing import Callable, List, Optional
