@@ -235,3 +235,56 @@ def test_guard_bands_separate_every_region_and_fit_the_size_hint():
             g0, n = guards[(name, par)]
             nxt = spans[i + 1][0] if i + 1 < len(spans) else c.bytes_used
             assert off <= g0 and n >= GUARD_BYTES and g0 + n == nxt     # band = [end of region, next region)
+
+
+def test_fp8_block_quantisation_round_trips_within_e4m3_precision():
+    """1x128 row scales and 128x128 weight scales: scale = amax / 448, the quantised block uses the
+    full e4m3 range, and dequantisation returns every value within e4m3's relative step (2^-3 of
+    the value, plus half the smallest subnormal step of the block)."""
+    import torch
+    from gpu_data_transfer_profile_b200.ops import gemm as G
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(20, 384, generator=g) * torch.logspace(-2, 2, 20)[:, None]
+    x[3] = 0                                           # an all-zero row keeps a finite, positive scale
+    q, s = G.quantize_rows_1x128(x)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (20, 3) and bool((s > 0).all())
+    back = q.float().view(20, 3, 128) * s[..., None]
+    err = (back - x.view(20, 3, 128)).abs()
+    bound = x.view(20, 3, 128).abs() * 0.0625 + s[..., None] * 2.0 ** -9
+    assert bool((err <= bound * 1.001).all())
+    nz = [r for r in range(20) if r != 3]
+    assert bool((q.float().view(20, 3, 128)[nz].abs().amax(-1) == 448).all())   # amax maps onto the top code
+    w = torch.randn(2, 256, 384, generator=g)
+    wq, ws = G.quantize_weights_128x128(w)
+    assert ws.shape == (2, 2, 3)
+    wb = G.dequantize_weights_128x128(wq, ws)
+    assert bool(((wb - w).abs() <= w.abs() * 0.0625 + ws.max() * 2.0 ** -9).all())
+
+
+def test_ep_cli_argument_validation_names_the_flag():
+    import argparse
+    from gpu_data_transfer_profile_b200.bench import ep_common as C
+    ap = argparse.ArgumentParser()
+    C.add_ep_flags(ap)
+    base = ["--num-local-tokens", "64", "--token-hidden", "256", "--num-of-experts", "8", "--topk", "2", "--ep", "2"]
+    C.validate_args(ap.parse_args(base), 2)
+    C.validate_args(ap.parse_args(base), 4)            # EP groups of 2 inside a world of 4
+    for edit, world, word in ((["--ep", "3"], 2, "--ep"), (["--topk", "9"], 2, "--topk"),
+                              (["--num-of-experts", "7"], 2, "--num-of-experts"),
+                              (["--token-hidden", "12"], 2, "16 bytes"),
+                              (["--no-async-finish", "--allocate-on-comm-stream"], 2, "--async-finish"),
+                              (["--benchmark-iters", "0"], 2, "--benchmark-iters")):
+        with pytest.raises(ValueError, match=word):
+            C.validate_args(ap.parse_args(base + edit), world)
+
+
+def test_clock_sample_summary_takes_the_loaded_half_and_names_reasons():
+    from gpu_data_transfer_profile_b200.utils.clocks import parse_clock_csv
+    head = "index, clocks.sm [MHz], clocks.max.sm [MHz], power.draw [W], active, hw, hwt, swt, swp\n"
+    idle = "0, 345, 1965, 180.0, 0x0, Not Active, Not Active, Not Active, Not Active\n"
+    busy = "0, 1950, 1965, 900.0, 0x4, Not Active, Not Active, Not Active, Active\n"
+    d = parse_clock_csv(head + idle * 3 + busy * 5)
+    assert d["sm_mhz"] == 1950 and d["sm_max_mhz"] == 1965 and d["reasons"] == ["sw_power_cap"] and d["samples"] == 8
+    hot = "0, 1200, 1965, 950.0, 0x40, Not Active, Active, Not Active, Not Active\n"
+    assert "hw_thermal_slowdown" in parse_clock_csv(busy + hot)["reasons"]
+    assert parse_clock_csv("garbage\n")["sm_mhz"] is None
