@@ -37,7 +37,8 @@ def reference_arm(args) -> int:
         why = "deep_ep importable but the reference tree is not installed under baseline/_ref"
     except Exception:
         pass
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if int(os.environ.get("RANK", "0")) == 0:        # one line per job, also under a multi-rank launch
+        print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
 

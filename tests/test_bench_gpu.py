@@ -34,3 +34,11 @@ def test_bench_one_gpu_flags(extra):
 def test_bench_reference_arm_is_unavailable():
     d = _run(["--impl", "reference"])
     assert d["impl"] == "reference" and "unavailable" in d
+
+
+def test_bench_reference_arm_prints_once_per_job():
+    """Launched as several ranks (as the driver does for N > 1), only rank 0 prints the line."""
+    env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
+    r = subprocess.run([sys.executable, "bench.py", "--impl", "reference", "--gpus", "2"], cwd=ROOT, env=env,
+                       capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and r.stdout.strip() == ""
