@@ -50,10 +50,16 @@ class SymmetricRegion:
         return t
 
     def close(self):
+        """Unmap the peers, then free this rank's allocation. The CUDA runtime leaves it undefined
+        what happens when an exported allocation is freed while another process still has it
+        mapped, so every rank first closes its mappings of the peers, all ranks meet on the host,
+        and only then does anyone free."""
         self._views = {}
         if self.local_ptr:
             for p in self._opened:
                 self.C.ipc_close(p)
+            if self._opened:
+                self.world.host_barrier()       # every importer has closed before any exporter frees
             self._opened = []
             self.C.symm_free(self.local_ptr)
             self.local_ptr = 0
